@@ -1,0 +1,152 @@
+/*
+ * b200_q4f16.h -- C ABI of the B200 (sm_100a) q4f16 dequantize+matmul kernel library.
+ *
+ * This is the drop-in boundary for ONE path of tlc-pack/relax: the group-quantized
+ * matmul that its fusion pipeline leaves as a fused `decode -> matmul -> astype`
+ * PrimFunc (uint32-packed int4 weights, fp16 scales per 32 elements of K, zero point 7).
+ * Every entry point is `extern "C"`, takes plain pointers and sizes (or DLPack tensors,
+ * which are plain C structs), never allocates device memory unless stated, launches on
+ * the stream it is given and returns without synchronising.
+ *
+ * Data layout (all row-major, contiguous):
+ *     x       fp16   [M, K]
+ *     wq      uint32 [N, K/8]    element k of row n sits in bits 4*(k%8).. of word k/8
+ *     scales  fp16   [N, K/32]
+ *     y       fp16   [M, N]      y = x . w^T,  w[n,k] = fp16(q[n,k]-7) * scales[n,k/32]
+ * fp32 accumulation; the dequantised weight is rounded to fp16 exactly once, as the
+ * reference's TIR does, so `b200_q4f16_dequantize` is bit-exact against it.
+ *
+ * Error convention (mirrors the reference's packed-function convention,
+ * include/tvm/runtime/c_runtime_api.h:238,355-363): 0 on success; a negative B200_E*
+ * code after storing a thread-local message readable with b200_last_error().  Nothing
+ * is launched when validation fails.  There is no CPU fallback: without a CUDA device
+ * of compute capability 10.x every compute entry point returns B200_ENODEVICE.
+ */
+#ifndef B200_Q4F16_H_
+#define B200_Q4F16_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_EINVAL (-1)     /* bad shape, dtype, alignment, null pointer */
+#define B200_ENODEVICE (-2)  /* no sm_100 device / CUDA runtime error before launch */
+#define B200_ELAUNCH (-3)    /* the launch itself was rejected by the CUDA runtime */
+#define B200_EDEVICE (-4)    /* a kernel reported a device-side error flag (bounded wait ran out) */
+#define B200_ENOTREADY (-5)  /* communicator / workspace not initialised */
+
+/* ---- DLPack tensor view (binary compatible with DLTensor of dlpack.h v0.x/1.x) ------------
+ * The reference passes tensors to packed functions as DLTensor* / NDArray handles
+ * (include/tvm/runtime/ndarray.h:85-188, include/tvm/runtime/packed_func.h:577-586). */
+typedef struct {
+  int32_t device_type; /* 2 = kDLCUDA, 1 = kDLCPU, 3 = kDLCUDAHost */
+  int32_t device_id;
+} B200DLDevice;
+typedef struct {
+  uint8_t code; /* 0 int, 1 uint, 2 float */
+  uint8_t bits;
+  uint16_t lanes;
+} B200DLDataType;
+typedef struct {
+  void* data;
+  B200DLDevice device;
+  int32_t ndim;
+  B200DLDataType dtype;
+  int64_t* shape;
+  int64_t* strides; /* NULL = compact row-major */
+  uint64_t byte_offset;
+} B200DLTensor;
+
+/* ---- library state --------------------------------------------------------------------- */
+
+/* Message of the last failing call on this thread ("" if none).  Replaces TVMGetLastError
+ * (include/tvm/runtime/c_runtime_api.h:229-238) for callers outside TVM. */
+B200_API const char* b200_last_error(void);
+
+/* ABI version of this header: major*100 + minor. */
+B200_API int b200_abi_version(void);
+
+/* Sets / reads the stream that the DLPack and packed entry points launch on for the calling
+ * thread.  Mirrors CUDAThreadEntry::ThreadLocal()->stream set through TVMSetStream
+ * (src/runtime/cuda/cuda_common.h:55-66, src/runtime/cuda/cuda_device_api.cc:209-211).
+ * NULL is the legacy default stream, as in the reference. */
+B200_API int b200_set_stream(void* cuda_stream);
+B200_API void* b200_get_stream(void);
+
+/* ---- kernels on raw device pointers ---------------------------------------------------- */
+
+/* w_out fp16 [N,K] = decode(wq, scales).  Replaces the `decode` PrimFunc the reference
+ * compiles from generic TIR ops (src/tir/op/op.cc:564 right_shift, :606 bitwise_and, :282
+ * cast) when decode and matmul stay two kernels.  Bit-exact.  K % 32 == 0. */
+B200_API int b200_q4f16_dequantize(const void* wq, const void* scales, void* w_out, int64_t N, int64_t K,
+                          void* cuda_stream);
+
+/* y = x . decode(wq, scales)^T.  Replaces the fused decode+matmul+astype PrimFunc
+ * (FuseTIR output, src/relax/transform/fuse_tir.cc:708-711; matmul semantics
+ * python/tvm/relax/transform/legalize_ops.py:203-264; astype :157-162).
+ * Picks the kernel family from M: the streaming skinny kernel for M <= 16, the tcgen05 /
+ * TMEM tensor-core kernel above that.  K % 32 == 0; pointers 16-byte aligned. */
+B200_API int b200_q4f16_matmul(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
+                      int64_t K, void* cuda_stream);
+
+/* The two families, callable directly (same contract as b200_q4f16_matmul).
+ * b200_q4f16_gemv requires 1 <= M <= 16. */
+B200_API int b200_q4f16_gemv(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
+                    int64_t K, void* cuda_stream);
+B200_API int b200_q4f16_gemm(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
+                    int64_t K, void* cuda_stream);
+
+/* Same matmul with the activation and the result in HOST memory (pinned memory makes the
+ * copies asynchronous): copies x to `x_dev`, runs the kernel, copies `y_dev` back to y_host,
+ * all on `cuda_stream`.  x_dev / y_dev are caller-owned device staging buffers of M*K and M*N
+ * fp16.  The weights stay on the device, as parameters do in the reference's VM
+ * (python/tvm/relax/vm.py:620-629). */
+B200_API int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, const void* scales, void* y_dev,
+                           void* y_host, int64_t M, int64_t N, int64_t K, void* cuda_stream);
+
+/* ---- DLPack entry points (destination-passing style) ------------------------------------
+ * What a `R.call_tir("b200.q4f16_matmul", (x, wq, scales), out_sinfo)` call reaches: inputs
+ * first, pre-allocated output last (src/relax/transform/call_tir_rewrite.cc:94-110).  They
+ * validate dtype, rank, shape agreement, compactness, device and alignment exactly as a
+ * contrib library must (cf. src/runtime/contrib/cublas/cublas.cc:211-267) and launch on the
+ * thread's current stream (b200_set_stream). */
+B200_API int b200_q4f16_matmul_dl(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales,
+                         B200DLTensor* y);
+B200_API int b200_q4f16_dequantize_dl(const B200DLTensor* wq, const B200DLTensor* scales, B200DLTensor* w_out);
+
+/* ---- packed-function symbols of the reference's C backend ABI ---------------------------
+ * Signature TVMBackendPackedCFunc (include/tvm/runtime/c_backend_api.h:49-51); the form the
+ * reference's BYOC C wrapper emits (src/relay/backend/contrib/codegen_c/codegen_c.h:101-112).
+ * `args` is an array of 8-byte TVMValue unions, tensors arrive as v_handle with type code
+ * 7 (kTVMDLTensorHandle) or 13 (kTVMNDArrayHandle).  Arguments: (x, wq, scales, y) and
+ * (wq, scales, w_out).  Return 0, or -1 with the message available from b200_last_error()
+ * (a TVM build forwards it with TVMAPISetLastError). */
+B200_API int32_t b200_q4f16_matmul_packed(void* args, int* type_codes, int num_args, void* out_value,
+                                 int* out_type_code, void* resource_handle);
+B200_API int32_t b200_q4f16_dequantize_packed(void* args, int* type_codes, int num_args, void* out_value,
+                                     int* out_type_code, void* resource_handle);
+
+/* ---- introspection used by tests and the benchmark --------------------------------------- */
+
+/* Number of kernels this library has launched on the calling thread since the last reset. */
+B200_API int64_t b200_launch_count(void);
+B200_API void b200_reset_launch_count(void);
+
+/* Selects a kernel variant / tuning knob by name (e.g. "gemv.warps"); returns B200_EINVAL for
+ * an unknown name or value.  Intended for benchmarking sweeps; defaults are the tuned ones. */
+B200_API int b200_set_option(const char* name, int64_t value);
+B200_API int64_t b200_get_option(const char* name);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_Q4F16_H_ */

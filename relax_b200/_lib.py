@@ -1,0 +1,103 @@
+"""ctypes binding of the C ABI declared in include/b200_q4f16.h.
+
+The library is the product; there is no fallback.  If the shared object is missing the
+import of :mod:`relax_b200` still works (so the build step can run) but every call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200_q4f16.so")
+
+OK, EINVAL, ENODEVICE, ELAUNCH, EDEVICE, ENOTREADY = 0, -1, -2, -3, -4, -5
+
+
+class B200Error(RuntimeError):
+    """Raised when an entry point returns a non-zero status; carries the code."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[b200 {code}] {msg}")
+        self.code = code
+        self.message = msg
+
+
+class DLDevice(ctypes.Structure):
+    _fields_ = [("device_type", ctypes.c_int32), ("device_id", ctypes.c_int32)]
+
+
+class DLDataType(ctypes.Structure):
+    _fields_ = [("code", ctypes.c_uint8), ("bits", ctypes.c_uint8), ("lanes", ctypes.c_uint16)]
+
+
+class DLTensor(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("device", DLDevice),
+        ("ndim", ctypes.c_int32),
+        ("dtype", DLDataType),
+        ("shape", ctypes.POINTER(ctypes.c_int64)),
+        ("strides", ctypes.POINTER(ctypes.c_int64)),
+        ("byte_offset", ctypes.c_uint64),
+    ]
+
+
+# name -> (restype, argtypes); one entry per prototype in include/b200_q4f16.h
+_vp, _i64, _ci = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+_dlp = ctypes.POINTER(DLTensor)
+_ip = ctypes.POINTER(ctypes.c_int)
+PROTOTYPES = {
+    "b200_last_error": (ctypes.c_char_p, []),
+    "b200_abi_version": (_ci, []),
+    "b200_set_stream": (_ci, [_vp]),
+    "b200_get_stream": (_vp, []),
+    "b200_q4f16_dequantize": (_ci, [_vp, _vp, _vp, _i64, _i64, _vp]),
+    "b200_q4f16_matmul": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_gemv": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_gemm": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_matmul_host": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_matmul_dl": (_ci, [_dlp, _dlp, _dlp, _dlp]),
+    "b200_q4f16_dequantize_dl": (_ci, [_dlp, _dlp, _dlp]),
+    "b200_q4f16_matmul_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
+    "b200_q4f16_dequantize_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
+    "b200_launch_count": (_i64, []),
+    "b200_reset_launch_count": (None, []),
+    "b200_set_option": (_ci, [ctypes.c_char_p, _i64]),
+    "b200_get_option": (_i64, [ctypes.c_char_p]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built (python -m relax_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200Error(ENODEVICE, f"{LIB_PATH} is missing: build it with `python -m relax_b200.build`; "
+                            "there is no fallback implementation")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(handle, name)  # AttributeError if the .so lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return lib().b200_last_error().decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise B200Error(rc, last_error())
+
+
+def set_option(name: str, value: int) -> None:
+    check(lib().b200_set_option(name.encode(), int(value)))
+
+
+def get_option(name: str) -> int:
+    return int(lib().b200_get_option(name.encode()))

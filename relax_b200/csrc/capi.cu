@@ -1,0 +1,327 @@
+// C ABI of the kernel library: argument validation, kernel-family dispatch, error state.
+// Everything a caller outside this library may bind is declared in include/b200_q4f16.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "internal.h"
+
+namespace b200 {
+
+namespace {
+thread_local char g_err[512] = {0};
+thread_local int64_t g_launches = 0;
+thread_local cudaStream_t g_stream = nullptr;
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void count_launch(int n) { g_launches += n; }
+
+Options& options() {
+  static Options o;
+  return o;
+}
+
+// Per-process cache of "device d is usable" (index = device ordinal).
+int ensure_device() {
+  static int ok[64] = {0};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(B200_ENODEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+  if (dev >= 0 && dev < 64 && ok[dev]) return B200_OK;
+  cudaDeviceProp p;
+  e = cudaGetDeviceProperties(&p, dev);
+  if (e != cudaSuccess) return fail(B200_ENODEVICE, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+  if (p.major != 10)
+    return fail(B200_ENODEVICE, "device %d is sm_%d%d; this library is built for sm_100a only and has no fallback",
+                dev, p.major, p.minor);
+  if (dev >= 0 && dev < 64) ok[dev] = 1;
+  return B200_OK;
+}
+
+int sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
+  }
+  return n[dev];
+}
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_common(const char* who, const void* wq, const void* scales, int64_t N, int64_t K) {
+  if (N < 0 || K < 0) return fail(B200_EINVAL, "%s: negative size N=%lld K=%lld", who, (long long)N, (long long)K);
+  if (K % 32 != 0) return fail(B200_EINVAL, "%s: K=%lld is not a multiple of the group size 32", who, (long long)K);
+  if (N > 0x7fffffffLL / 32 || K > 0x3fffffffLL)
+    return fail(B200_EINVAL, "%s: N=%lld K=%lld exceeds the supported range", who, (long long)N, (long long)K);
+  if (N > 0 && K > 0) {
+    if (!wq || !scales) return fail(B200_EINVAL, "%s: null weight or scale pointer", who);
+    if (!aligned16(wq)) return fail(B200_EINVAL, "%s: packed weights must be 16-byte aligned", who);
+    if (reinterpret_cast<uintptr_t>(scales) & 1u) return fail(B200_EINVAL, "%s: scales must be 2-byte aligned", who);
+  }
+  return B200_OK;
+}
+
+int check_matmul(const char* who, const void* x, const void* wq, const void* scales, const void* y, int64_t M,
+                 int64_t N, int64_t K) {
+  if (M < 0) return fail(B200_EINVAL, "%s: negative M=%lld", who, (long long)M);
+  int rc = check_common(who, wq, scales, N, K);
+  if (rc) return rc;
+  if (M > 0x7fffffffLL / 64) return fail(B200_EINVAL, "%s: M=%lld exceeds the supported range", who, (long long)M);
+  if (M > 0 && K > 0 && (!x || !aligned16(x))) return fail(B200_EINVAL, "%s: x must be non-null and 16-byte aligned", who);
+  if (M > 0 && N > 0 && (!y || (reinterpret_cast<uintptr_t>(y) & 1u)))
+    return fail(B200_EINVAL, "%s: y must be non-null and 2-byte aligned", who);
+  return B200_OK;
+}
+
+// y = 0 when the reduction is empty (K == 0): the sum over no terms.
+int zero_output(void* y, int64_t M, int64_t N, cudaStream_t s) {
+  if (M * N == 0) return B200_OK;
+  cudaError_t e = cudaMemsetAsync(y, 0, (size_t)(M * N) * 2, s);
+  if (e != cudaSuccess) return fail(B200_ELAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+enum Family { kAuto, kGemv, kGemm };
+
+int matmul_impl(Family fam, const char* who, const void* x, const void* wq, const void* scales, void* y, int64_t M,
+                int64_t N, int64_t K, void* stream) {
+  int rc = check_matmul(who, x, wq, scales, y, M, N, K);
+  if (rc) return rc;
+  if (fam == kGemv && (M < 1 || M > 16))
+    return fail(B200_EINVAL, "%s: the skinny kernel takes 1 <= M <= 16, got %lld", who, (long long)M);
+  rc = ensure_device();
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M == 0 || N == 0) return B200_OK;
+  if (K == 0) return zero_output(y, M, N, s);
+  bool use_gemv = fam == kGemv || (fam == kAuto && M <= 16);
+  auto xh = static_cast<const __half*>(x);
+  auto wh = static_cast<const uint32_t*>(wq);
+  auto sh = static_cast<const __half*>(scales);
+  auto yh = static_cast<__half*>(y);
+  if (use_gemv) return launch_gemv(xh, wh, sh, yh, M, N, K, s);
+  return launch_gemm(xh, wh, sh, yh, M, N, K, s);
+}
+
+// ---- DLPack validation -------------------------------------------------------------------
+bool is_dtype(const B200DLTensor* t, int code, int bits) {
+  return t->dtype.code == code && t->dtype.bits == bits && t->dtype.lanes == 1;
+}
+
+int check_tensor(const char* who, const char* name, const B200DLTensor* t, int code, int bits, int* dev) {
+  if (!t) return fail(B200_EINVAL, "%s: %s is null", who, name);
+  if (t->ndim != 2) return fail(B200_EINVAL, "%s: %s must have 2 dimensions, has %d", who, name, t->ndim);
+  if (!t->shape) return fail(B200_EINVAL, "%s: %s has no shape", who, name);
+  if (!is_dtype(t, code, bits))
+    return fail(B200_EINVAL, "%s: %s must be %s%d, got code=%d bits=%d lanes=%d", who, name,
+                code == 2 ? "float" : "uint", bits, t->dtype.code, t->dtype.bits, t->dtype.lanes);
+  if (t->device.device_type != 2 /* kDLCUDA */)
+    return fail(B200_EINVAL, "%s: %s is not on a CUDA device (device_type=%d)", who, name, t->device.device_type);
+  if (*dev < 0) *dev = t->device.device_id;
+  else if (*dev != t->device.device_id)
+    return fail(B200_EINVAL, "%s: %s is on device %d, other arguments on device %d", who, name, t->device.device_id, *dev);
+  if (t->strides) {  // compact row-major only (strides of size-1 dimensions are free)
+    int64_t expect = 1;
+    for (int i = 1; i >= 0; --i) {
+      if (t->shape[i] != 1 && t->strides[i] != expect)
+        return fail(B200_EINVAL, "%s: %s is not contiguous", who, name);
+      expect *= t->shape[i];
+    }
+  }
+  if (t->shape[0] < 0 || t->shape[1] < 0) return fail(B200_EINVAL, "%s: %s has a negative extent", who, name);
+  return B200_OK;
+}
+
+void* data_ptr(const B200DLTensor* t) { return static_cast<char*>(t->data) + t->byte_offset; }
+
+int check_current_device(const char* who, int dev) {
+  int cur = -1;
+  cudaError_t e = cudaGetDevice(&cur);
+  if (e != cudaSuccess) return fail(B200_ENODEVICE, "%s: no CUDA device: %s", who, cudaGetErrorString(e));
+  if (cur != dev)
+    return fail(B200_EINVAL, "%s: tensors live on device %d but the current device is %d", who, dev, cur);
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_err; }
+int b200_abi_version(void) { return 100; }
+
+int b200_set_stream(void* s) {
+  g_stream = static_cast<cudaStream_t>(s);
+  return B200_OK;
+}
+void* b200_get_stream(void) { return g_stream; }
+
+int64_t b200_launch_count(void) { return g_launches; }
+void b200_reset_launch_count(void) { g_launches = 0; }
+
+int b200_set_option(const char* name, int64_t v) {
+  if (!name) return fail(B200_EINVAL, "set_option: null name");
+  Options& o = options();
+  if (!strcmp(name, "gemv.variant")) { if (v < 0 || v > 2) return fail(B200_EINVAL, "gemv.variant in 0..2"); o.gemv_variant = v; }
+  else if (!strcmp(name, "gemv.warps")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.warps in 0..16"); o.gemv_warps = v; }
+  else if (!strcmp(name, "gemv.stages")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.stages in 0..16"); o.gemv_stages = v; }
+  else if (!strcmp(name, "gemv.pdl")) { o.gemv_pdl = v != 0; }
+  else if (!strcmp(name, "gemm.variant")) { if (v < 0 || v > 4) return fail(B200_EINVAL, "gemm.variant in 0..4"); o.gemm_variant = v; }
+  else if (!strcmp(name, "gemm.stages")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemm.stages in 0..8"); o.gemm_stages = v; }
+  else return fail(B200_EINVAL, "set_option: unknown option '%s'", name);
+  return B200_OK;
+}
+
+int64_t b200_get_option(const char* name) {
+  if (!name) return -1;
+  Options& o = options();
+  if (!strcmp(name, "gemv.variant")) return o.gemv_variant;
+  if (!strcmp(name, "gemv.warps")) return o.gemv_warps;
+  if (!strcmp(name, "gemv.stages")) return o.gemv_stages;
+  if (!strcmp(name, "gemv.pdl")) return o.gemv_pdl;
+  if (!strcmp(name, "gemm.variant")) return o.gemm_variant;
+  if (!strcmp(name, "gemm.stages")) return o.gemm_stages;
+  return -1;
+}
+
+int b200_q4f16_dequantize(const void* wq, const void* scales, void* w_out, int64_t N, int64_t K, void* stream) {
+  int rc = check_common("q4f16_dequantize", wq, scales, N, K);
+  if (rc) return rc;
+  if (N > 0 && K > 0 && (!w_out || !aligned16(w_out)))
+    return fail(B200_EINVAL, "q4f16_dequantize: output must be non-null and 16-byte aligned");
+  rc = ensure_device();
+  if (rc) return rc;
+  return launch_dequantize(static_cast<const uint32_t*>(wq), static_cast<const __half*>(scales),
+                           static_cast<__half*>(w_out), N, K, static_cast<cudaStream_t>(stream));
+}
+
+int b200_q4f16_matmul(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                      void* stream) {
+  return matmul_impl(kAuto, "q4f16_matmul", x, wq, scales, y, M, N, K, stream);
+}
+int b200_q4f16_gemv(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                    void* stream) {
+  return matmul_impl(kGemv, "q4f16_gemv", x, wq, scales, y, M, N, K, stream);
+}
+int b200_q4f16_gemm(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                    void* stream) {
+  return matmul_impl(kGemm, "q4f16_gemm", x, wq, scales, y, M, N, K, stream);
+}
+
+int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, const void* scales, void* y_dev,
+                           void* y_host, int64_t M, int64_t N, int64_t K, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return fail(B200_EINVAL, "q4f16_matmul_host: negative size");
+  if ((M * K > 0 && (!x_host || !x_dev)) || (M * N > 0 && (!y_host || !y_dev)))
+    return fail(B200_EINVAL, "q4f16_matmul_host: null host or staging buffer");
+  int rc = check_matmul("q4f16_matmul_host", x_dev, wq, scales, y_dev, M, N, K);
+  if (rc) return rc;
+  rc = ensure_device();
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (M * K > 0) {
+    e = cudaMemcpyAsync(x_dev, x_host, (size_t)(M * K) * 2, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return fail(B200_ELAUNCH, "q4f16_matmul_host: H2D copy: %s", cudaGetErrorString(e));
+  }
+  rc = matmul_impl(kAuto, "q4f16_matmul_host", x_dev, wq, scales, y_dev, M, N, K, stream);
+  if (rc) return rc;
+  if (M * N > 0) {
+    e = cudaMemcpyAsync(y_host, y_dev, (size_t)(M * N) * 2, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return fail(B200_ELAUNCH, "q4f16_matmul_host: D2H copy: %s", cudaGetErrorString(e));
+  }
+  return B200_OK;
+}
+
+int b200_q4f16_matmul_dl(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales, B200DLTensor* y) {
+  const char* who = "b200.q4f16_matmul";
+  int dev = -1, rc;
+  if ((rc = check_tensor(who, "x", x, 2, 16, &dev))) return rc;
+  if ((rc = check_tensor(who, "wq", wq, 1, 32, &dev))) return rc;
+  if ((rc = check_tensor(who, "scales", scales, 2, 16, &dev))) return rc;
+  if ((rc = check_tensor(who, "y", y, 2, 16, &dev))) return rc;
+  int64_t M = x->shape[0], K = x->shape[1], N = wq->shape[0];
+  if (K % 32 != 0) return fail(B200_EINVAL, "%s: K=%lld is not a multiple of the group size 32", who, (long long)K);
+  if (wq->shape[1] != K / 8)
+    return fail(B200_EINVAL, "%s: wq is [%lld,%lld], expected [N,%lld] for K=%lld", who, (long long)wq->shape[0],
+                (long long)wq->shape[1], (long long)(K / 8), (long long)K);
+  if (scales->shape[0] != N || scales->shape[1] != K / 32)
+    return fail(B200_EINVAL, "%s: scales is [%lld,%lld], expected [%lld,%lld]", who, (long long)scales->shape[0],
+                (long long)scales->shape[1], (long long)N, (long long)(K / 32));
+  if (y->shape[0] != M || y->shape[1] != N)
+    return fail(B200_EINVAL, "%s: y is [%lld,%lld], expected [%lld,%lld]", who, (long long)y->shape[0],
+                (long long)y->shape[1], (long long)M, (long long)N);
+  if ((rc = check_current_device(who, dev))) return rc;
+  return matmul_impl(kAuto, who, data_ptr(x), data_ptr(wq), data_ptr(scales), data_ptr(y), M, N, K, g_stream);
+}
+
+int b200_q4f16_dequantize_dl(const B200DLTensor* wq, const B200DLTensor* scales, B200DLTensor* w_out) {
+  const char* who = "b200.q4f16_dequantize";
+  int dev = -1, rc;
+  if ((rc = check_tensor(who, "wq", wq, 1, 32, &dev))) return rc;
+  if ((rc = check_tensor(who, "scales", scales, 2, 16, &dev))) return rc;
+  if ((rc = check_tensor(who, "w", w_out, 2, 16, &dev))) return rc;
+  int64_t N = wq->shape[0], K = wq->shape[1] * 8;
+  if (K % 32 != 0) return fail(B200_EINVAL, "%s: K=%lld is not a multiple of the group size 32", who, (long long)K);
+  if (scales->shape[0] != N || scales->shape[1] != K / 32)
+    return fail(B200_EINVAL, "%s: scales is [%lld,%lld], expected [%lld,%lld]", who, (long long)scales->shape[0],
+                (long long)scales->shape[1], (long long)N, (long long)(K / 32));
+  if (w_out->shape[0] != N || w_out->shape[1] != K)
+    return fail(B200_EINVAL, "%s: output is [%lld,%lld], expected [%lld,%lld]", who, (long long)w_out->shape[0],
+                (long long)w_out->shape[1], (long long)N, (long long)K);
+  if ((rc = check_current_device(who, dev))) return rc;
+  return b200_q4f16_dequantize(data_ptr(wq), data_ptr(scales), data_ptr(w_out), N, K, g_stream);
+}
+
+// ---- packed-function symbols (legacy TVM C backend ABI) ------------------------------------
+// TVMValue is an 8-byte union; tensors come as v_handle with type code 7 or 13.
+static int packed_tensors(const char* who, void* args, int* type_codes, int num_args, int want,
+                          const B200DLTensor** out) {
+  if (num_args != want) return fail(B200_EINVAL, "%s: expected %d arguments, got %d", who, want, num_args);
+  if (!args || !type_codes) return fail(B200_EINVAL, "%s: null argument array", who);
+  void** vals = static_cast<void**>(args);
+  for (int i = 0; i < want; ++i) {
+    if (type_codes[i] != 7 && type_codes[i] != 13)
+      return fail(B200_EINVAL, "%s: argument %d has type code %d, expected a tensor (7 or 13)", who, i, type_codes[i]);
+    out[i] = static_cast<const B200DLTensor*>(vals[i]);
+  }
+  return B200_OK;
+}
+
+int32_t b200_q4f16_matmul_packed(void* args, int* type_codes, int num_args, void* out_value, int* out_type_code,
+                                 void* resource_handle) {
+  (void)out_value; (void)resource_handle;
+  const B200DLTensor* t[4];
+  if (packed_tensors("b200.q4f16_matmul", args, type_codes, num_args, 4, t)) return -1;
+  if (b200_q4f16_matmul_dl(t[0], t[1], t[2], const_cast<B200DLTensor*>(t[3]))) return -1;
+  if (out_type_code) *out_type_code = 4;  // kTVMNullptr: DPS functions return nothing
+  return 0;
+}
+
+int32_t b200_q4f16_dequantize_packed(void* args, int* type_codes, int num_args, void* out_value, int* out_type_code,
+                                     void* resource_handle) {
+  (void)out_value; (void)resource_handle;
+  const B200DLTensor* t[3];
+  if (packed_tensors("b200.q4f16_dequantize", args, type_codes, num_args, 3, t)) return -1;
+  if (b200_q4f16_dequantize_dl(t[0], t[1], const_cast<B200DLTensor*>(t[2]))) return -1;
+  if (out_type_code) *out_type_code = 4;
+  return 0;
+}
+
+}  // extern "C"

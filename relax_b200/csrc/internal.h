@@ -1,0 +1,38 @@
+// Host-side declarations shared by the translation units of the kernel library.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200_q4f16.h"
+
+namespace b200 {
+
+// Stores a printf-formatted message for b200_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+void count_launch(int n = 1);
+
+// Tuning knobs (b200_set_option).  Plain ints; read at launch time.
+struct Options {
+  int64_t gemv_variant = 0;   // 0 = auto, 1 = register-streaming kernel, 2 = bulk-copy pipelined kernel
+  int64_t gemv_warps = 0;     // 0 = auto
+  int64_t gemv_stages = 0;    // 0 = auto (bulk-copy pipeline depth)
+  int64_t gemv_pdl = 1;       // programmatic dependent launch on the streaming kernels
+  int64_t gemm_variant = 0;   // 0 = auto
+  int64_t gemm_stages = 0;
+};
+Options& options();
+
+// Kernel launchers: arguments validated by the caller, pointers are device pointers.
+int launch_dequantize(const uint32_t* wq, const __half* scales, __half* w, int64_t N, int64_t K,
+                      cudaStream_t stream);
+int launch_gemv(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                int64_t K, cudaStream_t stream);
+int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                int64_t K, cudaStream_t stream);
+
+// Device capability check, cached per device; 0 when the current device is sm_100.
+int ensure_device();
+int sm_count();
+
+}  // namespace b200

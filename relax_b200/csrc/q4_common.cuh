@@ -1,0 +1,61 @@
+// Shared device helpers for the q4f16 kernels (sm_100a).
+//
+// Decode rule (what the reference's TIR computes, src/tir/op/op.cc:564,606,282 in the
+// reference tree): q = (word >> 4*(k%8)) & 0xF, w = fp16(q - 7) * scale with ONE fp16
+// round-to-nearest-even multiply.  The helpers below form (q - 7) exactly in fp16 with the
+// "magic number" trick (OR the nibble into the mantissa of 1024.0, subtract) and then issue
+// exactly one HMUL2 per pair, so every kernel that uses them reproduces the reference's
+// dequantised weights bit for bit.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace b200 {
+
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) {
+  return *reinterpret_cast<__half2*>(&v);
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) {
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One packed word (8 nibbles, k0 lowest) -> four half2 of exact (q-7):
+//   out[0] = (k0,k4)  out[1] = (k1,k5)  out[2] = (k2,k6)  out[3] = (k3,k7)
+// 1 shift + 4 LOP3 + 4 half2 arithmetic ops.
+__device__ __forceinline__ void q4_unpack_pairs(uint32_t w, __half2 (&out)[4]) {
+  const uint32_t kMagic = 0x64006400u;                 // (1024, 1024)
+  const __half2 kSub = u32_as_h2(0x64076407u);         // (1031, 1031)
+  const __half2 kSixteenth = u32_as_h2(0x2C002C00u);   // (1/16, 1/16)
+  const __half2 kNeg71 = u32_as_h2(0xD470D470u);       // (-71, -71)
+  uint32_t lo0 = (w & 0x000F000Fu) | kMagic;           // 1024 + q0      , 1024 + q4
+  uint32_t hi0 = (w & 0x00F000F0u) | kMagic;           // 1024 + 16*q1   , 1024 + 16*q5
+  uint32_t w8 = w >> 8;
+  uint32_t lo1 = (w8 & 0x000F000Fu) | kMagic;          // q2, q6
+  uint32_t hi1 = (w8 & 0x00F000F0u) | kMagic;          // q3, q7
+  out[0] = __hsub2(u32_as_h2(lo0), kSub);                    // exact: q - 7
+  out[1] = __hfma2(u32_as_h2(hi0), kSixteenth, kNeg71);      // exact: (64 + q) - 71
+  out[2] = __hsub2(u32_as_h2(lo1), kSub);
+  out[3] = __hfma2(u32_as_h2(hi1), kSixteenth, kNeg71);
+}
+
+// Same, followed by the single rounding multiply by the group's scale (both lanes = scale).
+__device__ __forceinline__ void q4_dequant_pairs(uint32_t w, __half2 scale2, uint32_t (&out)[4]) {
+  __half2 v[4];
+  q4_unpack_pairs(w, v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = h2_as_u32(__hmul2(v[i], scale2));
+}
+
+// Dequantised word in natural order: out = (k0,k1) (k2,k3) (k4,k5) (k6,k7).
+__device__ __forceinline__ uint4 q4_dequant_natural(uint32_t w, __half2 scale2) {
+  uint32_t p[4];
+  q4_dequant_pairs(w, scale2, p);
+  uint4 o;
+  o.x = __byte_perm(p[0], p[1], 0x5410);
+  o.y = __byte_perm(p[2], p[3], 0x5410);
+  o.z = __byte_perm(p[0], p[1], 0x7632);
+  o.w = __byte_perm(p[2], p[3], 0x7632);
+  return o;
+}
+
+}  // namespace b200

@@ -1,0 +1,167 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU oracle."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import relax_b200
+from relax_b200 import _lib, ops, synth
+from util import assert_bits_equal, assert_matmul_close, golden_cases
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(*arrs):
+    return [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in arrs]
+
+
+# ------------------------------------------------------------------------------ decode
+def test_dequantize_golden_bit_exact(cuda_lib, golden):
+    for name, x, wq, s, w, y in golden_cases(golden):
+        twq, ts = dev(wq, s)
+        out = ops.q4f16_dequantize(twq, ts)
+        assert_bits_equal(out.cpu().numpy(), w, name)
+
+
+@pytest.mark.parametrize("n,k", [(1, 32), (3, 96), (257, 1056), (4096, 4096), (1000, 11008)])
+def test_dequantize_bit_exact_random(cuda_lib, n, k):
+    _, wq, s = synth.make_case(1, n, k, seed=n + k)
+    twq, ts = dev(wq, s)
+    out = ops.q4f16_dequantize(twq, ts).cpu().numpy()
+    assert_bits_equal(out, oracle.c_dequantize(wq, s), f"decode {n}x{k}")
+
+
+def test_dequantize_all_scale_bit_patterns(cuda_lib):
+    # every finite fp16 scale (both signs, subnormals included) times every nibble value
+    bits = np.arange(0x10000, dtype=np.uint32)
+    bits = bits[(bits & 0x7C00) != 0x7C00].astype(np.uint16)      # drop inf/nan
+    n = bits.size
+    s = bits.view(np.float16).reshape(n, 1)
+    q = np.tile(np.arange(16, dtype=np.uint8), 2)[None, :].repeat(n, axis=0)
+    wq = oracle.pack_nibbles(q)
+    twq, ts = dev(wq, s)
+    out = ops.q4f16_dequantize(twq, ts).cpu().numpy()
+    assert_bits_equal(out, oracle.c_dequantize(wq, s), "all scales x all nibbles")
+
+
+def test_dequantize_empty(cuda_lib):
+    twq = torch.zeros((0, 16), dtype=torch.uint32, device="cuda")
+    ts = torch.zeros((0, 4), dtype=torch.float16, device="cuda")
+    assert ops.q4f16_dequantize(twq, ts).shape == (0, 128)
+
+
+# ------------------------------------------------------------------------------ skinny matmul
+def run_matmul(x, wq, s, family="auto"):
+    tx, twq, ts = dev(x, wq, s)
+    # canary-padded output: the kernel must write exactly M*N values
+    m, n = x.shape[0], wq.shape[0]
+    buf = torch.full((m * n + 64,), float("nan"), dtype=torch.float16, device="cuda")
+    out = buf[: m * n].view(m, n)
+    ops.q4f16_matmul(tx, twq, ts, out=out, family=family)
+    torch.cuda.synchronize()
+    assert torch.isnan(buf[m * n:]).all(), "kernel wrote past the end of y"
+    return out.cpu().numpy()
+
+
+def test_gemv_golden(cuda_lib, golden):
+    for name, x, wq, s, w, y in golden_cases(golden):
+        out = run_matmul(x, wq, s)
+        assert_matmul_close(out, x, wq, s, name, y_ref=y)
+
+
+@pytest.mark.parametrize("m", list(range(1, 17)))
+def test_gemv_every_m(cuda_lib, m):
+    x, wq, s = synth.make_case(m, 300, 1024, seed=m)
+    assert_matmul_close(run_matmul(x, wq, s), x, wq, s, f"M={m}")
+
+
+@pytest.mark.parametrize("n,k", [(1, 32), (15, 32), (16, 64), (17, 96), (33, 224), (100, 256), (129, 288),
+                                 (4096, 4096), (11008, 4096), (4096, 11008), (1280, 8192), (1024, 1376)])
+@pytest.mark.parametrize("m", [1, 3, 8, 16])
+def test_gemv_shapes(cuda_lib, m, n, k):
+    x, wq, s = synth.make_case(m, n, k, seed=7 * n + k + m)
+    assert_matmul_close(run_matmul(x, wq, s), x, wq, s, f"M={m} N={n} K={k}")
+
+
+def test_gemv_known_answers(cuda_lib):
+    k, n = 256, 48
+    rng = np.random.default_rng(5)
+    s = rng.uniform(0.005, 0.02, (n, k // 32)).astype(np.float16)
+    x = rng.standard_normal((2, k)).astype(np.float16)
+    for fill in (0x00000000, 0xFFFFFFFF, 0x77777777):   # all -7*s, all 8*s, all zero weights
+        wq = np.full((n, k // 8), fill, dtype=np.uint32)
+        out = run_matmul(x, wq, s)
+        assert_matmul_close(out, x, wq, s, f"fill {fill:#x}")
+    # one-hot x picks out single dequantised weights exactly (no summation involved)
+    q = rng.integers(0, 16, (n, k), dtype=np.uint8)
+    wq = oracle.pack_nibbles(q)
+    for pos in (0, 5, 31, 32, 100, k - 1):
+        xo = np.zeros((1, k), np.float16)
+        xo[0, pos] = 1.0
+        out = run_matmul(xo, wq, s)
+        assert_bits_equal(out[0], oracle.c_dequantize(wq, s)[:, pos], f"one-hot at {pos}")
+
+
+def test_gemv_warp_counts_agree(cuda_lib):
+    x, wq, s = synth.make_case(4, 500, 2048, seed=11)
+    try:
+        for w in (1, 2, 4, 8, 16):
+            relax_b200.set_option("gemv.warps", w)
+            assert_matmul_close(run_matmul(x, wq, s, family="gemv"), x, wq, s, f"warps={w}")
+    finally:
+        relax_b200.set_option("gemv.warps", 0)
+
+
+def test_matmul_k_zero_and_empty(cuda_lib):
+    x = torch.zeros((3, 0), dtype=torch.float16, device="cuda")
+    wq = torch.zeros((5, 0), dtype=torch.uint32, device="cuda")
+    s = torch.zeros((5, 0), dtype=torch.float16, device="cuda")
+    y = torch.full((3, 5), 7.0, dtype=torch.float16, device="cuda")
+    ops.q4f16_matmul(x, wq, s, out=y)
+    assert (y == 0).all()
+    x = torch.zeros((0, 64), dtype=torch.float16, device="cuda")
+    wq = torch.zeros((5, 8), dtype=torch.uint32, device="cuda")
+    s = torch.zeros((5, 2), dtype=torch.float16, device="cuda")
+    assert ops.q4f16_matmul(x, wq, s).shape == (0, 5)
+
+
+def test_packed_entry_point_runs_on_device(cuda_lib):
+    x, wq, s = synth.make_case(2, 64, 128, seed=2)
+    tx, twq, ts = dev(x, wq, s)
+    ty = torch.empty((2, 64), dtype=torch.float16, device="cuda")
+    views = [ops.to_dltensor(t) for t in (tx, twq, ts, ty)]
+    vals = (ctypes.c_void_p * 4)(*[ctypes.addressof(v.tensor) for v in views])
+    codes = (ctypes.c_int * 4)(7, 13, 7, 7)
+    out_code = ctypes.c_int(-1)
+    cuda_lib.b200_set_stream(torch.cuda.current_stream().cuda_stream)
+    rc = cuda_lib.b200_q4f16_matmul_packed(vals, codes, 4, None, ctypes.byref(out_code), None)
+    assert rc == 0, _lib.last_error()
+    assert out_code.value == 4
+    torch.cuda.synchronize()
+    assert_matmul_close(ty.cpu().numpy(), x, wq, s, "packed")
+
+
+def test_host_buffer_entry_point(cuda_lib):
+    x, wq, s = synth.make_case(4, 256, 512, seed=9)
+    _, twq, ts = dev(x, wq, s)
+    xh = torch.from_numpy(x).pin_memory()
+    yh = torch.empty((4, 256), dtype=torch.float16).pin_memory()
+    xd = torch.empty((4, 512), dtype=torch.float16, device="cuda")
+    yd = torch.empty((4, 256), dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rc = cuda_lib.b200_q4f16_matmul_host(xh.data_ptr(), xd.data_ptr(), twq.data_ptr(), ts.data_ptr(), yd.data_ptr(),
+                                         yh.data_ptr(), 4, 256, 512, st)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    assert_matmul_close(yh.numpy(), x, wq, s, "host buffers")
+
+
+def test_launch_counter(cuda_lib):
+    x, wq, s = synth.make_case(1, 64, 128)
+    tx, twq, ts = dev(x, wq, s)
+    ops.reset_launch_count()
+    ops.q4f16_matmul(tx, twq, ts)
+    ops.q4f16_dequantize(twq, ts)
+    assert ops.launch_count() == 2
