@@ -141,6 +141,11 @@ B200_API int32_t b200_q4f16_dequantize_packed(void* args, int* type_codes, int n
 B200_API int64_t b200_launch_count(void);
 B200_API void b200_reset_launch_count(void);
 
+/* Reads (and clears) the device-side error word: non-zero when a kernel's bounded wait ran
+ * out and it gave up instead of spinning.  Synchronises the device; for tests and diagnosis.
+ * Returns the flag bits (>= 0) or a negative B200_E* code. */
+B200_API int b200_device_error_flags(void);
+
 /* Selects a kernel variant / tuning knob by name (e.g. "gemv.warps"); returns B200_EINVAL for
  * an unknown name or value.  Intended for benchmarking sweeps; defaults are the tuned ones. */
 B200_API int b200_set_option(const char* name, int64_t value);

@@ -63,6 +63,7 @@ PROTOTYPES = {
     "b200_q4f16_dequantize_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_launch_count": (_i64, []),
     "b200_reset_launch_count": (None, []),
+    "b200_device_error_flags": (_ci, []),
     "b200_set_option": (_ci, [ctypes.c_char_p, _i64]),
     "b200_get_option": (_i64, [ctypes.c_char_p]),
 }

@@ -17,8 +17,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200_q4f16.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-SOURCES = ["capi.cu", "dequant.cu", "gemv.cu", "gemm_tcgen05.cu"]
-HEADERS = ["internal.h", "q4_common.cuh"]
+SOURCES = ["capi.cu", "tmap.cu", "dequant.cu", "gemv.cu", "gemv_pipe.cu", "gemm_tcgen05.cu"]
+HEADERS = ["internal.h", "q4_common.cuh", "sm100_ptx.cuh", "tmap.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -134,7 +134,7 @@ int check_tensor(const char* who, const char* name, const B200DLTensor* t, int c
   if (*dev < 0) *dev = t->device.device_id;
   else if (*dev != t->device.device_id)
     return fail(B200_EINVAL, "%s: %s is on device %d, other arguments on device %d", who, name, t->device.device_id, *dev);
-  if (t->strides) {  // compact row-major only (strides of size-1 dimensions are free)
+  if (t->strides && t->shape[0] != 0 && t->shape[1] != 0) {  // compact row-major only (strides of size-1 dimensions are free)
     int64_t expect = 1;
     for (int i = 1; i >= 0; --i) {
       if (t->shape[i] != 1 && t->strides[i] != expect)
@@ -175,6 +175,13 @@ void* b200_get_stream(void) { return g_stream; }
 
 int64_t b200_launch_count(void) { return g_launches; }
 void b200_reset_launch_count(void) { g_launches = 0; }
+
+int b200_device_error_flags(void) {
+  int rc = ensure_device();
+  if (rc) return rc;
+  if (cudaDeviceSynchronize() != cudaSuccess) return fail(B200_EDEVICE, "device_error_flags: %s", cudaGetErrorString(cudaGetLastError()));
+  return device_error_flags_read_and_clear();
+}
 
 int b200_set_option(const char* name, int64_t v) {
   if (!name) return fail(B200_EINVAL, "set_option: null name");

@@ -4,4 +4,6 @@ namespace b200 {
 int launch_gemm(const __half*, const uint32_t*, const __half*, __half*, int64_t M, int64_t, int64_t, cudaStream_t) {
   return fail(B200_EINVAL, "q4f16_gemm: M=%lld: tensor-core kernel not built yet", (long long)M);
 }
+int gemm_error_read_and_clear() { return 0; }
+int device_error_flags_read_and_clear() { return gemv_pipe_error_read_and_clear() | (gemm_error_read_and_clear() << 8); }
 }  // namespace b200

@@ -273,9 +273,17 @@ int launch_gemv_stream(const __half* x, const uint32_t* wq, const __half* scales
   return launch_stream<16, 1>(x, wq, scales, y, m, n, k, stream);
 }
 
+int launch_gemv_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                     int64_t K, cudaStream_t stream);
+
 int launch_gemv(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream) {
   if (N == 0 || M == 0) return B200_OK;
+  const int64_t variant = options().gemv_variant;
+  if (variant != 1) {
+    int rc = launch_gemv_pipe(x, wq, scales, y, M, N, K, stream);
+    if (rc != B200_ENOTREADY) return rc;   // ENOTREADY = shape outside the pipelined kernel's domain
+  }
   return launch_gemv_stream(x, wq, scales, y, M, N, K, stream);
 }
 

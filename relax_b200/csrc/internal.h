@@ -31,6 +31,11 @@ int launch_gemv(const __half* x, const uint32_t* wq, const __half* scales, __hal
 int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
 
+// Reads and clears the per-kernel device error words (bit 0-7: skinny pipeline, 8-15: tensor-core GEMM).
+int device_error_flags_read_and_clear();
+int gemv_pipe_error_read_and_clear();
+int gemm_error_read_and_clear();
+
 // Device capability check, cached per device; 0 when the current device is sm_100.
 int ensure_device();
 int sm_count();

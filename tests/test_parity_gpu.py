@@ -104,18 +104,67 @@ def test_gemv_known_answers(cuda_lib):
         assert_bits_equal(out[0], oracle.c_dequantize(wq, s)[:, pos], f"one-hot at {pos}")
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (1, 100, 256), (2, 37, 1280), (4, 4096, 11008), (7, 333, 2304),
+                                   (8, 2000, 11008), (13, 500, 4096), (16, 4096, 4096), (16, 1280, 8192),
+                                   (16, 700, 11008), (16, 20000, 2048)])
+def test_gemv_both_kernels(cuda_lib, variant, m, n, k):
+    x, wq, s = synth.make_case(m, n, k, seed=n + k + m)
+    try:
+        relax_b200.set_option("gemv.variant", variant)
+        out = run_matmul(x, wq, s, family="gemv")
+    finally:
+        relax_b200.set_option("gemv.variant", 0)
+    assert_matmul_close(out, x, wq, s, f"variant={variant} M={m} N={n} K={k}")
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+@pytest.mark.parametrize("stages", [2, 3, 8, 16])
+def test_gemv_pipeline_depths(cuda_lib, stages):
+    x, wq, s = synth.make_case(3, 5000, 4096, seed=stages)
+    try:
+        relax_b200.set_option("gemv.stages", stages)
+        out = run_matmul(x, wq, s, family="gemv")
+    finally:
+        relax_b200.set_option("gemv.stages", 0)
+    assert_matmul_close(out, x, wq, s, f"stages={stages}")
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+def test_gemv_back_to_back_dependent_launches(cuda_lib):
+    # a chain y1 = W1 x, y2 = W2 y1, ... launched back to back: each launch may start (and
+    # prefetch its weights) before the previous one has finished, but must not read x early
+    n = k = 1024
+    rng = np.random.default_rng(3)
+    ws = [synth.make_weights(n, k, rng) for _ in range(6)]
+    x0 = (rng.standard_normal((1, k)) * 0.5).astype(np.float16)
+    dws = [dev(wq, s) for wq, s in ws]
+    bufs = [torch.from_numpy(x0).cuda()] + [torch.empty((1, n), dtype=torch.float16, device="cuda") for _ in ws]
+    for i, (twq, ts) in enumerate(dws):
+        ops.q4f16_matmul(bufs[i], twq, ts, out=bufs[i + 1], family="gemv")
+    torch.cuda.synchronize()
+    ref = x0
+    for i, (wq, s) in enumerate(ws):
+        got = bufs[i + 1].cpu().numpy()
+        assert_matmul_close(got, ref, wq, s, f"chain step {i}")
+        ref = got          # feed the kernel's own output forward so each step is checked in isolation
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
 def test_gemv_warp_counts_agree(cuda_lib):
     x, wq, s = synth.make_case(4, 500, 2048, seed=11)
     try:
         for w in (1, 2, 4, 8, 16):
             relax_b200.set_option("gemv.warps", w)
+            relax_b200.set_option("gemv.variant", 1)
             assert_matmul_close(run_matmul(x, wq, s, family="gemv"), x, wq, s, f"warps={w}")
     finally:
         relax_b200.set_option("gemv.warps", 0)
+        relax_b200.set_option("gemv.variant", 0)
 
 
 def test_matmul_k_zero_and_empty(cuda_lib):
-    x = torch.zeros((3, 0), dtype=torch.float16, device="cuda")
+    x = torch.zeros((3, 0), dtype=torch.float16, device="cuda")  # K == 0: the empty sum
     wq = torch.zeros((5, 0), dtype=torch.uint32, device="cuda")
     s = torch.zeros((5, 0), dtype=torch.float16, device="cuda")
     y = torch.full((3, 5), 7.0, dtype=torch.float16, device="cuda")
