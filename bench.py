@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the q4f16 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemv|prefill] [--impl reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of
+synthetic input:
+
+* ``gemv`` (default): the decode matmul of the first benchmark config (x fp16 [1,4096], W int4
+  [4096,4096] group 32), launched over ``copies`` DISTINCT weight sets back to back so that the
+  working set (copies x 9.45 MB) is several times the 126 MB L2 and every launch streams its
+  weights from HBM.  value = algorithmic bytes moved per second.
+* ``prefill``: the tensor-core dequant-GEMM of the second config (M=2048, N=11008, K=4096);
+  value = TFLOP/s.
+
+With --gpus N > 1 (launched under torchrun) every rank runs the same independent stream of
+matmuls on its own GPU (the matmul path shards by rows of W with no exchange): weak scaling,
+value = sum over ranks of bytes / max over ranks of time.
+
+``--impl reference`` times the CPU restatement of the reference's path (oracle/, OpenMP over all
+host cores) on the same config and metric; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+
+def algorithmic_bytes(m, n, k):
+    """Packed weights + scales + activation + output: what a launch must move at least."""
+    return n * k // 2 + n * (k // 32) * 2 + m * k * 2 + m * n * 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML every
+    5 ms when the bindings are importable, else with an `nvidia-smi -lms` child process."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def _nvml_loop(self):
+        import pynvml as nv
+
+        h = nv.nvmlDeviceGetHandleByIndex(self.index)
+        bad = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+               "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+               "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+               "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        self.nv_max = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        while not self.stop_flag:
+            self.nv_sm.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+            for name, bit in bad.items():
+                if r & bit:
+                    self.nv_reasons.add(name)
+            time.sleep(0.005)
+
+    def start(self):
+        self.stop_flag, self.nv_sm, self.nv_reasons, self.nv_max, self.nv_thread = False, [], set(), None, None
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            # NVML orders devices by PCI bus id; honour CUDA_VISIBLE_DEVICES remapping when it is a plain list
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                self.index = int(vis.split(",")[self.index])
+            self.nv_thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.nv_thread.start()
+            return
+        except Exception:
+            self.nv_thread = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.nv_thread is not None:
+            self.stop_flag = True
+            self.nv_thread.join(timeout=1.0)
+            return {"sm_mhz": float(np.median(self.nv_sm)) if self.nv_sm else None, "sm_max_mhz": self.nv_max,
+                    "reasons": sorted(self.nv_reasons), "samples": len(self.nv_sm), "via": "nvml"}
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_time_matmul(m, n, k, seed, budget_s=12.0, max_reps=50):
+    """Times the oracle (C restatement, all host threads) on one matmul; returns (s/matmul, threads, reps)."""
+    import oracle
+    from relax_b200 import synth
+
+    x, wq, s = synth.make_case(m, n, k, seed=seed)
+    threads = oracle.c_max_threads()
+    oracle.c_matmul(x, wq, s)  # warm-up (page faults, thread pool)
+    reps, t0 = 0, time.perf_counter()
+    while reps < max_reps and (time.perf_counter() - t0) < budget_s:
+        oracle.c_matmul(x, wq, s)
+        reps += 1
+    return (time.perf_counter() - t0) / reps, threads, reps
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    if args.workload == "gemv":
+        m, n, k = 1, 4096, 4096
+        times = []
+        for _ in range(args.warmup):
+            cpu_time_matmul(m, n, k, seed=0, budget_s=0.2, max_reps=2)
+        for _ in range(args.steps):
+            t, threads, reps = cpu_time_matmul(m, n, k, seed=0, budget_s=max(0.5, 20.0 / args.steps), max_reps=200)
+            times.append(t)
+        per = float(np.mean(times))
+        value = algorithmic_bytes(m, n, k) / per / 1e9
+        unit, metric = "GB/s", "q4f16 dequant-GEMV HBM GB/s"
+        sample = f"{args.steps} steps x up to 200 repeats of the full 1x4096x4096 matmul"
+        config = {"workload": "q4f16 decode GEMV M=1 N=4096 K=4096 group32"}
+    else:
+        m, n, k = 2048, 11008, 4096
+        ms = 64  # bounded sample: 64 of the 2048 rows of x; cost is linear in M
+        t, threads, reps = cpu_time_matmul(ms, n, k, seed=1, budget_s=20.0, max_reps=max(1, args.steps))
+        per = t * (m / ms)
+        value = 2.0 * m * n * k / per / 1e12
+        unit, metric = "TFLOP/s", "q4f16 prefill dequant-GEMM TFLOP/s"
+        sample = f"{ms} of {m} activation rows, time scaled linearly to M={m}"
+        config = {"workload": "q4f16 prefill dequant-GEMM M=2048 N=11008 K=4096 group32"}
+    line = {
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's LLVM path (oracle/q4f16_oracle.c), OpenMP over rows of W; "
+                "the reference itself cannot be built here (no LLVM, empty submodules)",
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from relax_b200 import _lib, ops, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+    peaks = measured_peaks()
+
+    if args.workload == "gemv":
+        m, n, k = 1, 4096, 4096
+        copies = args.copies
+        metric, unit = "q4f16 dequant-GEMV HBM GB/s", "GB/s"
+    else:
+        m, n, k = 2048, 11008, 4096
+        copies = 2
+        metric, unit = "q4f16 prefill dequant-GEMM TFLOP/s", "TFLOP/s"
+    if args.shape:
+        m, n, k = (int(v) for v in args.shape.split(","))
+    per_launch_bytes = algorithmic_bytes(m, n, k)
+    weights = [synth.make_weights_torch(n, k, 1000 * rank + i, dev) for i in range(copies)]
+    x_host = torch.from_numpy(synth.make_case(m, 8, k, seed=rank)[0]).pin_memory()
+    y_host = torch.empty((m, n), dtype=torch.float16).pin_memory()
+    x = x_host.to(dev)
+    ys = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(copies)]
+    stream = torch.cuda.Stream(device=dev)
+    sp = stream.cuda_stream
+
+    def step_device():
+        for (wq, s), y in zip(weights, ys):
+            rc = L.b200_q4f16_matmul(x.data_ptr(), wq.data_ptr(), s.data_ptr(), y.data_ptr(), m, n, k, sp)
+            if rc:
+                raise RuntimeError(_lib.last_error())
+
+    def step_e2e():
+        # the call a user of the plugin makes, with HOST activation and result buffers
+        for (wq, s), y in zip(weights, ys):
+            rc = L.b200_q4f16_matmul_host(x_host.data_ptr(), x.data_ptr(), wq.data_ptr(), s.data_ptr(), y.data_ptr(),
+                                          y_host.data_ptr(), m, n, k, sp)
+            if rc:
+                raise RuntimeError(_lib.last_error())
+
+    # One CUDA graph per step for the device-resident measurement (a 1.5 us kernel is shorter than
+    # a launch; a decoder replays exactly such a graph).
+    with torch.cuda.stream(stream):
+        step_device()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step_device()
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ops.reset_launch_count()
+    ms_total = timed(step_device if args.no_graph else graph.replay, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = args.steps * copies  # graph replays do not pass through the library's launch counter
+    ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup))
+    err = L.b200_device_error_flags()
+    if err:
+        raise RuntimeError(f"device error flags {err:#x}")
+
+    ms_per_step = ms_total / args.steps
+    us_per_launch = ms_per_step * 1e3 / copies
+    if args.workload == "gemv":
+        value = world * copies * per_launch_bytes / (ms_per_step * 1e-3) / 1e9
+        e2e_value = world * copies * per_launch_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+        achieved = per_launch_bytes / (us_per_launch * 1e-6) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                    "kernel": "q4f16_gemv_pipe_kernel", "us_per_launch": us_per_launch,
+                    "algorithmic_bytes_per_launch": per_launch_bytes}
+    else:
+        flops = 2.0 * m * n * k
+        value = world * copies * flops / (ms_per_step * 1e-3) / 1e12
+        e2e_value = world * copies * flops / (ms_e2e / args.steps * 1e-3) / 1e12
+        achieved = flops / (us_per_launch * 1e-6) / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"],
+                    "kernel": "q4f16_gemm_tcgen05_kernel", "us_per_launch": us_per_launch}
+
+    if rank == 0:
+        # CPU baseline on a bounded sample, rank 0, N=1 only
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            if args.workload == "gemv":
+                t, threads, reps = cpu_time_matmul(m, n, k, seed=0, budget_s=10.0, max_reps=300)
+                cpu = {"value": per_launch_bytes / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                       "sample": f"{reps} repeats of the full 1x4096x4096 matmul"}
+            else:
+                ms_ = 32
+                t, threads, reps = cpu_time_matmul(ms_, n, k, seed=1, budget_s=15.0, max_reps=3)
+                cpu = {"value": 2.0 * m * n * k / (t * m / ms_) / 1e12, "unit": "TFLOP/s", "cores": threads,
+                       "kind": "port", "sample": f"{ms_} of {m} activation rows, scaled linearly"}
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 (int4 weights, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"q4f16 {'decode GEMV' if args.workload == 'gemv' else 'prefill dequant-GEMM'} "
+                                   f"M={m} N={n} K={k} group32",
+                       "launches_per_step": copies,
+                       "l2": f"{copies} distinct weight sets ({copies * per_launch_bytes / 1e6:.0f} MB) rotate through "
+                             "each step, larger than the 126 MB L2"},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": copies * m * k * 2,
+                    "d2h_bytes_per_step": copies * m * n * 2},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", choices=["gemv", "prefill"], default="gemv")
+    ap.add_argument("--copies", type=int, default=40, help="distinct weight sets per step (gemv)")
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--shape", default=None, help="M,N,K override (profiling of other shapes of the same kernels)")
+    ap.add_argument("--no-graph", action="store_true", help="launch directly instead of replaying a CUDA graph")
+    args = ap.parse_args()
+    if args.steps is None:
+        args.steps = {"gemv": 1000, "prefill": 100}[args.workload] if args.impl == "b200" else 10
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_gpu(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

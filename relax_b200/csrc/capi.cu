@@ -190,8 +190,9 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "gemv.warps")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.warps in 0..16"); o.gemv_warps = v; }
   else if (!strcmp(name, "gemv.stages")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.stages in 0..16"); o.gemv_stages = v; }
   else if (!strcmp(name, "gemv.pdl")) { o.gemv_pdl = v != 0; }
-  else if (!strcmp(name, "gemm.variant")) { if (v < 0 || v > 4) return fail(B200_EINVAL, "gemm.variant in 0..4"); o.gemm_variant = v; }
+  else if (!strcmp(name, "gemm.variant")) { if (v < 0 || v > 63) return fail(B200_EINVAL, "gemm.variant in 0..63"); o.gemm_variant = v; }
   else if (!strcmp(name, "gemm.stages")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemm.stages in 0..8"); o.gemm_stages = v; }
+  else if (!strcmp(name, "gemm.max_ctas")) { if (v < 0 || v > 1024) return fail(B200_EINVAL, "gemm.max_ctas in 0..1024"); o.gemm_max_ctas = v; }
   else return fail(B200_EINVAL, "set_option: unknown option '%s'", name);
   return B200_OK;
 }
@@ -205,6 +206,7 @@ int64_t b200_get_option(const char* name) {
   if (!strcmp(name, "gemv.pdl")) return o.gemv_pdl;
   if (!strcmp(name, "gemm.variant")) return o.gemm_variant;
   if (!strcmp(name, "gemm.stages")) return o.gemm_stages;
+  if (!strcmp(name, "gemm.max_ctas")) return o.gemm_max_ctas;
   return -1;
 }
 

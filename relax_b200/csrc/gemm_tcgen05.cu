@@ -1,9 +1,387 @@
-// placeholder until the tcgen05 kernel lands in this file
+// Prefill q4f16 matmul on the 5th-generation tensor cores: y[M,N] = x[M,K] . decode(Wq,S)^T.
+//
+// Replaces the fused decode+matmul+astype PrimFunc of the reference for large M (reference:
+// python/tvm/relax/transform/legalize_ops.py:203-264 for the matmul semantics; its own GPU
+// route would be a MetaSchedule-tuned mma.sync kernel, src/relax/transform/meta_schedule.cc).
+// Tensor-core bound: 2*M*N*K flop against N*K/2 bytes of weights.
+//
+// One persistent CTA per SM, output tile 128 tokens x 256 weight rows, K in blocks of 64:
+//
+//   warp 0      TMA producer for x: box {64 k, 128 rows} fp16, 128-byte swizzle -> ring A
+//   warp 2      TMA producer for the packed weights (box {16 words = 128 k, 256 rows}, 64-byte
+//               swizzle) and, when the scale rows are 16-byte aligned, for the scales (box
+//               {8 groups = 256 k, 256 rows}) -> rings RAW / SC
+//   warps 8-15  dequantisers: thread r owns weight row r of the tile.  Per K block it turns 8
+//               packed words into 64 fp16 (exact q-7, one HMUL2 by the scale: the reference's
+//               rounding) and stores them as the 128-byte row r of the UMMA operand tile, chunk
+//               c at position c ^ (r % 8): the canonical K-major SWIZZLE_128B layout a TMA load
+//               would have produced -> ring B (generic-proxy stores, fence.proxy.async, mbarrier)
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16 (M=128, N=256,
+//               K=16) four times per K block, A and B from shared-memory descriptors, fp32
+//               accumulator in TMEM; tcgen05.commit hands the A and B stages back and, after the
+//               last K block, publishes the accumulator.  TMEM holds two 256-column accumulators
+//               so the epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 4-7   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, fp32 -> fp16 (RN), 16-byte
+//               global stores into row-major y.
+//
+// Out-of-range rows (M, N tails) and columns (K tail) are zero-filled by the TMA unit: a zero
+// scale makes the weight +-0, a zero x makes the product 0, the epilogue skips them.
+// Every mbarrier wait is bounded; a wait that runs out raises a block-wide abort flag and a
+// device error word, all loops then run through without waiting, TMEM is freed and the kernel ends.
 #include "internal.h"
+#include "q4_common.cuh"
+#include "sm100_ptx.cuh"
+#include "tmap.h"
+
 namespace b200 {
-int launch_gemm(const __half*, const uint32_t*, const __half*, __half*, int64_t M, int64_t, int64_t, cudaStream_t) {
-  return fail(B200_EINVAL, "q4f16_gemm: M=%lld: tensor-core kernel not built yet", (long long)M);
+
+__device__ int g_gemm_error = 0;
+
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;            // tokens per tile (UMMA M)
+constexpr int BN = 256;            // weight rows per tile (UMMA N)
+constexpr int BK = 64;             // k per MMA stage (one 128-byte swizzled row of fp16)
+constexpr int SA = 4;              // x stages
+constexpr int SB = 3;              // dequantised-weight stages
+constexpr int SR = 2;              // packed-weight stages (128 k each = two K blocks)
+constexpr int SS = 2;              // scale stages (256 k each = four K blocks)
+constexpr int kABytes = BM * BK * 2;          // 16384
+constexpr int kBBytes = BN * BK * 2;          // 32768
+constexpr int kRawBytes = BN * 64;            // 16384: 256 rows x 16 words
+constexpr int kScBytes = BN * 16;             // 4096:  256 rows x 8 scales
+constexpr int kNumThreads = 512;
+constexpr int kDequantWarps = 8;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint64_t kWaitNs = 4000000000ull;   // 4 s
+
+struct Smem {
+  // all operand buffers are multiples of 1024 bytes, the struct is placed 1024-aligned
+  unsigned char a[SA][kABytes];
+  unsigned char b[SB][kBBytes];
+  unsigned char raw[SR][kRawBytes];
+  unsigned char sc[SS][kScBytes];
+  uint64_t a_full[SA], a_empty[SA];
+  uint64_t b_full[SB], b_empty[SB];
+  uint64_t raw_full[SR], raw_empty[SR];
+  uint64_t sc_full[SS], sc_empty[SS];
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct GemmParams {
+  CUtensorMap tm_x;    // fp16   {K, M},     box {64, 128}, SWIZZLE_128B
+  CUtensorMap tm_w;    // uint32 {K/8, N},   box {16, 256}, SWIZZLE_64B
+  CUtensorMap tm_s;    // fp16   {K/32, N},  box {8, 256}   (only when scales_tma)
+  const __half* scales;
+  __half* y;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int scales_tma;
+};
+
+// Bounded wait that also honours (and raises) the block-wide abort flag.
+__device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (*abort_flag) return;
+  if (!mbar_wait_ns(bar, parity, kWaitNs)) {
+    *abort_flag = 1;
+    atomicExch(&g_gemm_error, code);
+  }
 }
-int gemm_error_read_and_clear() { return 0; }
+
+__global__ void __launch_bounds__(kNumThreads, 1)
+q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ unsigned char smem_unaligned[];
+  Smem& sm = *reinterpret_cast<Smem*>(smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u));
+  volatile int* abort_flag = &sm.abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    for (int i = 0; i < SA; ++i) { mbar_init(&sm.a_full[i], 1); mbar_init(&sm.a_empty[i], 1); }
+    for (int i = 0; i < SB; ++i) { mbar_init(&sm.b_full[i], kDequantWarps); mbar_init(&sm.b_empty[i], 1); }
+    for (int i = 0; i < SR; ++i) { mbar_init(&sm.raw_full[i], 1); mbar_init(&sm.raw_empty[i], kDequantWarps); }
+    for (int i = 0; i < SS; ++i) { mbar_init(&sm.sc_full[i], 1); mbar_init(&sm.sc_empty[i], kDequantWarps); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sm.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer: x
+    if (lane == 0) {
+      prefetch_tmap(&p.tm_x);
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int tm = tile % p.tiles_m;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % SA;
+          const uint32_t round = it / SA;
+          if (round > 0) wait_or_abort(&sm.a_empty[s], (round - 1) & 1, abort_flag, 1);
+          mbar_arrive_expect_tx(&sm.a_full[s], kABytes);
+          tma_load_2d(sm.a[s], &p.tm_x, kb * BK, tm * BM, &sm.a_full[s]);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ TMA producer: packed W, scales
+    if (lane == 0) {
+      prefetch_tmap(&p.tm_w);
+      if (p.scales_tma) prefetch_tmap(&p.tm_s);
+      uint32_t it_raw = 0, it_sc = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int tn = tile / p.tiles_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (p.scales_tma && (kb & 3) == 0) {
+            const int s = it_sc % SS;
+            const uint32_t round = it_sc / SS;
+            if (round > 0) wait_or_abort(&sm.sc_empty[s], (round - 1) & 1, abort_flag, 2);
+            mbar_arrive_expect_tx(&sm.sc_full[s], kScBytes);
+            tma_load_2d(sm.sc[s], &p.tm_s, (kb >> 2) * 8, tn * BN, &sm.sc_full[s]);
+            ++it_sc;
+          }
+          if ((kb & 1) == 0) {
+            const int s = it_raw % SR;
+            const uint32_t round = it_raw / SR;
+            if (round > 0) wait_or_abort(&sm.raw_empty[s], (round - 1) & 1, abort_flag, 3);
+            mbar_arrive_expect_tx(&sm.raw_full[s], kRawBytes);
+            tma_load_2d(sm.raw[s], &p.tm_w, (kb >> 1) * 16, tn * BN, &sm.raw_full[s]);
+            ++it_raw;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16_f32(BM, BN);
+      uint32_t it_a = 0, it_b = 0, it_acc = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it_acc) {
+        const int acc = it_acc & 1;
+        const uint32_t acc_round = it_acc >> 1;
+        if (acc_round > 0) wait_or_abort(&sm.acc_empty[acc], (acc_round - 1) & 1, abort_flag, 4);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it_a, ++it_b) {
+          const int sa = it_a % SA, sb = it_b % SB;
+          wait_or_abort(&sm.a_full[sa], (it_a / SA) & 1, abort_flag, 5);
+          wait_or_abort(&sm.b_full[sb], (it_b / SB) & 1, abort_flag, 6);
+          tc_fence_after_sync();
+          const uint64_t da = umma_desc_k128(smem_u32(sm.a[sa]));
+          const uint64_t db = umma_desc_k128(smem_u32(sm.b[sb]));
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16) {
+            // advancing 16 fp16 along K inside the swizzled 128-byte row = +32 bytes = +2 in the
+            // descriptor's 16-byte address units
+            umma_f16_ss(d_tmem, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, (kb | k16) != 0);
+          }
+          umma_commit(&sm.a_empty[sa]);
+          umma_commit(&sm.b_empty[sb]);
+        }
+        umma_commit(&sm.acc_full[acc]);
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ------------------------------------------------------------------ epilogue
+    const int ew = warp - 4;                       // TMEM lane quadrant this warp may read
+    uint32_t it_acc = 0;
+    const bool vec_ok = (p.N % 8) == 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it_acc) {
+      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      const int acc = it_acc & 1;
+      wait_or_abort(&sm.acc_full[acc], (it_acc >> 1) & 1, abort_flag, 7);
+      tc_fence_after_sync();
+      const int row = tm * BM + ew * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          __half* dst = p.y + (int64_t)row * p.N + col0;
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1])));
+              o.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])));
+              o.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])));
+              o.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+              *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (col0 + q < p.N) dst[q] = __float2half_rn(__uint_as_float(v[q]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.acc_empty[acc]);
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ dequantisers
+    const int r = tid - 256;                        // weight row inside the tile, 0..255
+    const int r8 = r & 7;
+    uint32_t it_raw = 0, it_sc = 0, it_b = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int tn = tile / p.tiles_m;
+      const int grow = tn * BN + r;                 // global weight row (may be >= N: zero-filled)
+      uint4 sc4 = make_uint4(0, 0, 0, 0);           // 8 scales of the current 256-k span
+      uint4 pk[4];                                  // 16 packed words of the current 128-k span
+      for (int kb = 0; kb < num_kb; ++kb, ++it_b) {
+        if ((kb & 3) == 0) {
+          if (p.scales_tma) {
+            const int s = it_sc % SS;
+            wait_or_abort(&sm.sc_full[s], (it_sc / SS) & 1, abort_flag, 8);
+            sc4 = *reinterpret_cast<const uint4*>(sm.sc[s] + r * 16);
+            pin_loaded(sc4);
+            fence_proxy_async_smem();              // generic reads ordered before the TMA refill (async proxy)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.sc_empty[s]);
+            ++it_sc;
+          } else {
+            // scale rows not 16-byte aligned: plain loads, zero past the ends
+            const int G = p.K >> 5;
+            uint32_t w[4] = {0, 0, 0, 0};
+            if (grow < p.N) {
+              const __half* srow = p.scales + (int64_t)grow * G;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                int gi = (kb >> 2) * 8 + j;
+                uint32_t bits = gi < G ? (uint32_t)__half_as_ushort(__ldg(srow + gi)) : 0u;
+                w[j >> 1] |= bits << (16 * (j & 1));
+              }
+            }
+            sc4 = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        if ((kb & 1) == 0) {
+          const int s = it_raw % SR;
+          wait_or_abort(&sm.raw_full[s], (it_raw / SR) & 1, abort_flag, 9);
+          // row r holds 64 bytes = 4 chunks of 16; 64-byte swizzle: chunk ^= (r >> 1) & 3
+          const unsigned char* rr = sm.raw[s] + r * 64;
+          const int x = (r >> 1) & 3;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rr + ((c ^ x) << 4));
+#pragma unroll
+          for (int c = 0; c < 4; ++c) pin_loaded(pk[c]);   // loads returned before the stage is released
+          fence_proxy_async_smem();              // generic reads ordered before the TMA refill (async proxy)
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.raw_empty[s]);
+          ++it_raw;
+        }
+        // ---- this K block: words 8*(kb&1) .. +7 of pk, scale groups 2*(kb&3), 2*(kb&3)+1
+        const int sb = it_b % SB;
+        const uint32_t b_round = it_b / SB;
+        if (b_round > 0) wait_or_abort(&sm.b_empty[sb], (b_round - 1) & 1, abort_flag, 10);
+        const uint32_t scw = (kb & 2) ? ((kb & 1) ? sc4.w : sc4.z) : ((kb & 1) ? sc4.y : sc4.x);
+        const __half2 scp = u32_as_h2(scw);
+        const __half2 s_lo = __half2(__low2half(scp), __low2half(scp));
+        const __half2 s_hi = __half2(__high2half(scp), __high2half(scp));
+        const uint4 p0 = (kb & 1) ? pk[2] : pk[0];
+        const uint4 p1 = (kb & 1) ? pk[3] : pk[1];
+        unsigned char* brow = sm.b[sb] + r * 128;     // 8-row atoms of 1024 B, rows 128 B apart
+        const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 o = q4_dequant_natural(words[c], c < 4 ? s_lo : s_hi);
+          *reinterpret_cast<uint4*>(brow + ((c ^ r8) << 4)) = o;
+        }
+        fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.b_full[sb]);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    // loads may still be in flight into this CTA's shared memory: let them land before it is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                int64_t K, cudaStream_t stream) {
+  if (M == 0 || N == 0) return B200_OK;
+  GemmParams p;
+  int rc;
+  {
+    const uint64_t d[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t s[1] = {(uint64_t)K * 2};
+    const uint32_t b[2] = {BK, BM};
+    if ((rc = make_tmap(&p.tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  }
+  {
+    const uint64_t d[2] = {(uint64_t)(K / 8), (uint64_t)N};
+    const uint64_t s[1] = {(uint64_t)(K / 2)};
+    const uint32_t b[2] = {16, BN};
+    if ((rc = make_tmap(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, wq, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+  }
+  p.scales_tma = (K % 256 == 0) && ((reinterpret_cast<uintptr_t>(scales) & 15u) == 0);
+  if (p.scales_tma) {
+    const uint64_t d[2] = {(uint64_t)(K / 32), (uint64_t)N};
+    const uint64_t s[1] = {(uint64_t)(K / 32) * 2};
+    const uint32_t b[2] = {8, BN};
+    if ((rc = make_tmap(&p.tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scales, d, s, b, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+  } else {
+    p.tm_s = p.tm_w;   // unused
+  }
+  p.scales = scales;
+  p.y = y;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_n = (int)((N + BN - 1) / BN);
+  const int tiles = p.tiles_m * p.tiles_n;
+  int grid = sm_count();
+  if (options().gemm_max_ctas > 0 && grid > options().gemm_max_ctas) grid = (int)options().gemm_max_ctas;
+  if (grid > tiles) grid = tiles;
+  const size_t smem = sizeof(Smem) + 1024;
+  auto kern = q4f16_gemm_tcgen05_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemm: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
+  kern<<<grid, kNumThreads, smem, stream>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemm launch: %s", cudaGetErrorString(e));
+  count_launch();
+  return B200_OK;
+}
+
+int gemm_error_read_and_clear() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return 0xff;
+  if (v) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+  return v & 0xff;
+}
+
 int device_error_flags_read_and_clear() { return gemv_pipe_error_read_and_clear() | (gemm_error_read_and_clear() << 8); }
+
 }  // namespace b200

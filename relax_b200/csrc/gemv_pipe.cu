@@ -155,7 +155,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
             if (round > 0) {
               // Legitimately as long as the previous kernel in the stream runs (the consumers
               // that free the stages sit in griddepcontrol.wait until then): bound it by time.
-              if (*(volatile int*)&s_abort || !mbar_wait_ns(&empty[s], (round - 1) & 1, kProducerWaitNs)) {
+              if (*(volatile int*)&s_abort || !mbar_wait_ns_relaxed(&empty[s], (round - 1) & 1, kProducerWaitNs)) {
                 atomicExch(&g_gemv_pipe_error, 1);
                 *(volatile int*)&s_abort = 1;
                 return;   // copies already issued land in stages the consumers still own
@@ -246,6 +246,14 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
             sc1[j] = *reinterpret_cast<const __half*>(st + kWBytes + (c * kRows + g + 8) * 16 + u * 2);
           }
           if (half == 1) {
+            // the loads must have returned before the stage goes back to the producer
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              pin_loaded(w0[j]);
+              pin_loaded(w1[j]);
+              pin_loaded((uint32_t)__half_as_ushort(sc0[j]) | ((uint32_t)__half_as_ushort(sc1[j]) << 16));
+            }
+            fence_proxy_async_smem();   // generic reads ordered before the TMA refill (async proxy)
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);            // all of the stage is in registers: hand it back
           }
@@ -331,7 +339,7 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   p.M = M; p.N = N; p.K = K;
   p.ntiles = (N + kRows - 1) / kRows;
   int stages = (int)options().gemv_stages;
-  if (stages <= 0) stages = 4;
+  if (stages <= 0) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
   const size_t kMaxSmem = 227 * 1024;

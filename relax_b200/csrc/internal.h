@@ -20,6 +20,7 @@ struct Options {
   int64_t gemv_pdl = 1;       // programmatic dependent launch on the streaming kernels
   int64_t gemm_variant = 0;   // 0 = auto
   int64_t gemm_stages = 0;
+  int64_t gemm_max_ctas = 0;  // 0 = one per SM; smaller values force several tiles per CTA (tests)
 };
 Options& options();
 

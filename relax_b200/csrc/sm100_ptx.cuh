@@ -58,6 +58,18 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // Wait bounded by wall time (and by an iteration count): for waits whose legitimate length is
 // set by something outside the kernel, e.g. a producer that runs ahead of a programmatic
 // dependent launch and must wait for the previous kernel in the stream to finish.
+// Same with a sleep between polls: for waits that are off the critical path (a producer waiting
+// for a free stage), so that the polling does not compete with the working warps for issue slots.
+__device__ __forceinline__ bool mbar_wait_ns_relaxed(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1; i < 0x7fffffffu; ++i) {
+    __nanosleep(100);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 127u) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+  }
+  return false;
+}
 __device__ __forceinline__ bool mbar_wait_ns(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
@@ -139,6 +151,17 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 // ---- programmatic dependent launch --------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Releasing a shared-memory stage back to a TMA producer after reading it with ordinary loads:
+// the refill is an async-proxy write, the reads are generic-proxy accesses, and the mbarrier
+// arrive alone did not keep them apart (observed on B200: a warp occasionally got the NEXT fill
+// of the stage in the registers it had loaded before arriving).  The sequence used everywhere is
+//   loads; pin_loaded(values); fence.proxy.async.shared::cta; __syncwarp(); lane 0 arrives.
+// pin_loaded keeps the compiler from sinking the loads below the fence.
+__device__ __forceinline__ void pin_loaded(const uint4& v) {
+  asm volatile("" ::"r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void pin_loaded(uint32_t v) { asm volatile("" ::"r"(v) : "memory"); }
 
 // ---- named barriers ---------------------------------------------------------------------------
 __device__ __forceinline__ void bar_sync(int id, int nthreads) {

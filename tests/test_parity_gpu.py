@@ -214,3 +214,107 @@ def test_launch_counter(cuda_lib):
     ops.q4f16_matmul(tx, twq, ts)
     ops.q4f16_dequantize(twq, ts)
     assert ops.launch_count() == 2
+
+
+# ------------------------------------------------------------------------------ tensor-core matmul
+def test_gemm_one_hot_rows_select_weights_exactly(cuda_lib):
+    # x row m is one-hot at k_m: y[m, n] = w[n, k_m] with no summation, so the result must equal the
+    # reference's dequantised weight bit for bit.  Exercises every position of the swizzled operand
+    # tiles (k_m sweeps 0..K-1) and both halves of every scale group.
+    n, k = 256, 256
+    m = k
+    rng = np.random.default_rng(17)
+    wq, s = synth.make_weights(n, k, rng)
+    x = np.zeros((m, k), np.float16)
+    x[np.arange(m), np.arange(k)] = 1.0
+    out = run_matmul(x, wq, s, family="gemm")
+    assert_bits_equal(out, oracle.c_dequantize(wq, s).T.copy(), "one-hot rows")
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+def test_gemm_one_hot_weights_select_activations(cuda_lib):
+    # every weight row has a single non-zero weight (q=8 -> +1 * scale=1 at k_n, q=7 -> 0 elsewhere):
+    # y[m, n] = x[m, k_n] exactly.  Checks the x-side tile layout and the accumulator/epilogue mapping.
+    m, n, k = 128, 256, 128
+    rng = np.random.default_rng(18)
+    q = np.full((n, k), 7, np.uint8)
+    kn = rng.integers(0, k, n)
+    q[np.arange(n), kn] = 8
+    wq = oracle.pack_nibbles(q)
+    s = np.ones((n, k // 32), np.float16)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    out = run_matmul(x, wq, s, family="gemm")
+    assert_bits_equal(out, x[:, kn].copy(), "one-hot weights")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (256, 512, 512), (17, 256, 128), (129, 300, 96),
+                                   (200, 264, 1376), (384, 1000, 2048), (1024, 1280, 8192), (130, 11008, 4096),
+                                   (2048, 520, 4096)])
+def test_gemm_shapes(cuda_lib, m, n, k):
+    x, wq, s = synth.make_case(m, n, k, seed=m + n + k)
+    out = run_matmul(x, wq, s, family="gemm")
+    assert_matmul_close(out, x, wq, s, f"gemm M={m} N={n} K={k}")
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+def test_gemm_matches_gemv_family(cuda_lib):
+    # the two kernel families on the same problem (M=16 is in both domains)
+    x, wq, s = synth.make_case(16, 512, 1024, seed=3)
+    a = run_matmul(x, wq, s, family="gemm")
+    b = run_matmul(x, wq, s, family="gemv")
+    assert_matmul_close(a, x, wq, s, "gemm@16")
+    assert_matmul_close(b, x, wq, s, "gemv@16")
+
+
+def test_prefill_config_full_size(cuda_lib):
+    # second benchmark config at full size: sampled rows against the oracle, then properties that
+    # need no oracle: linearity in x and agreement with matmul over the library's own decode.
+    m, n, k = 2048, 11008, 4096
+    x, wq, s = synth.make_case(m, n, k, seed=2)
+    tx, twq, ts = dev(x, wq, s)
+    y = ops.q4f16_matmul(tx, twq, ts)
+    torch.cuda.synchronize()
+    assert cuda_lib.b200_device_error_flags() == 0
+    yh = y.cpu().numpy()
+    rng = np.random.default_rng(0)
+    rows = np.sort(rng.choice(n, 96, replace=False))
+    toks = np.sort(rng.choice(m, 64, replace=False))
+    assert_matmul_close(yh[np.ix_(toks, rows)], x[toks], wq[rows], s[rows], "cfg2 sample")
+    # (2x) . W == 2 (x . W): scaling by two commutes with every rounding in the path except where the
+    # fp16 result is subnormal (|y| < 2^-14), where it may differ by one subnormal step
+    y2 = ops.q4f16_matmul(tx * 2, twq, ts)
+    normal = y.abs() >= 2.0 ** -13
+    assert torch.equal(y2[normal], (y * 2)[normal])
+    assert ((y2.float() - 2 * y.float()).abs()[~normal] <= 2.0 ** -23).all()
+    # against a dense fp32 matmul over the bit-exact decode, on a slab
+    w = ops.q4f16_dequantize(twq[:512].contiguous(), ts[:512].contiguous()).float()
+    ref = (tx.float() @ w.t())
+    err = (y[:, :512].float() - ref).abs().max().item()
+    assert err < 0.05, err
+
+
+@pytest.mark.parametrize("k,tiles,ctas", [(256, 16, 4), (512, 16, 4), (1024, 12, 3), (4096, 8, 1)])
+def test_gemm_many_tiles_per_cta_bit_exact(cuda_lib, k, tiles, ctas):
+    # Few CTAs, many tiles each: the shared-memory rings wrap many times and tiles follow each other
+    # inside one CTA (accumulator double buffering, stage reuse across tile boundaries).  One-hot
+    # activations make every output a single dequantised weight, so any stage that is refilled or
+    # read at the wrong moment shows up as a bit difference.  Repeated, because such races are
+    # timing dependent.
+    m, n = 128, 256 * tiles
+    rng = np.random.default_rng(k + tiles)
+    wq, s = synth.make_weights(n, k, rng)
+    w = oracle.c_dequantize(wq, s)
+    twq, ts = dev(wq, s)
+    try:
+        relax_b200.set_option("gemm.max_ctas", ctas)
+        for kbase in range(0, k, 128):
+            x = np.zeros((m, k), np.float16)
+            x[np.arange(128), kbase + np.arange(128)] = 1.0
+            tx = torch.from_numpy(x).cuda()
+            want = np.ascontiguousarray(w[:, kbase:kbase + 128].T)
+            for _ in range(3 if k <= 1024 else 1):
+                out = ops.q4f16_matmul(tx, twq, ts, family="gemm").cpu().numpy()
+                assert_bits_equal(out, want, f"K={k} kbase={kbase}")
+    finally:
+        relax_b200.set_option("gemm.max_ctas", 0)
+    assert cuda_lib.b200_device_error_flags() == 0
