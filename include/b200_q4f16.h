@@ -135,6 +135,35 @@ B200_API int32_t b200_q4f16_matmul_packed(void* args, int* type_codes, int num_a
 B200_API int32_t b200_q4f16_dequantize_packed(void* args, int* type_codes, int num_args, void* out_value,
                                      int* out_type_code, void* resource_handle);
 
+/* ---- glue kernels of a decode step (around the quantised matmuls) --------------------------
+ * The reference has no RMSNorm / RoPE / attention op; these compute the composition of its
+ * elementwise ops (mean, sqrt, divide, multiply, softmax, silu: python/tvm/relax/transform/
+ * legalize_ops.py:378-381,506-514) with fp32 statistics and one fp16 rounding at each output.
+ * All pointers are device pointers; `pos` points at one int32 (the position of the token being
+ * decoded, read on the device so that a captured CUDA graph can be replayed for every position). */
+
+/* y[b,:] = rmsnorm(x[b,:]) * w.  If delta != NULL, x += delta first (x is updated in place: the
+ * residual stream).  x, delta, y fp16 [B,H]; w fp16 [H]; H % 8 == 0, H <= 16384. */
+B200_API int b200_rmsnorm(void* x, const void* delta, const void* w, void* y, int64_t B, int64_t H, float eps,
+                          void* cuda_stream);
+
+/* Rotary embedding of q and k (pairs i, i+64 of a 128-wide head; cos/sin fp32 [max_pos,64]), then k
+ * and v are stored in the caches at position *pos.  qkv fp16 [B, 3*nh*128] = [q | k | v];
+ * q_out fp16 [B, nh, 128]; caches fp16 [B, max_ctx, nh, 128]. */
+B200_API int b200_rope_kv_append(const void* qkv, const void* cos_t, const void* sin_t, const void* pos, void* q_out,
+                                 void* k_cache, void* v_cache, int64_t B, int64_t nh, int64_t max_ctx,
+                                 void* cuda_stream);
+
+/* out fp16 [B, nh*128] = softmax(q.K^T / sqrt(128)) . V over positions 0..*pos.  `scratch` is
+ * caller-owned device memory of b200_attn_decode_scratch_bytes(B, nh, max_ctx) bytes holding the
+ * per-chunk partial results (two launches: partials over 128-token chunks, then the merge). */
+B200_API int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t max_ctx);
+B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
+                              void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);
+
+/* out[b,i] = silu(gu[b,i]) * gu[b,I+i]; gu fp16 [B,2I], out fp16 [B,I]; I % 8 == 0. */
+B200_API int b200_silu_mul(const void* gu, void* out, int64_t B, int64_t I, void* cuda_stream);
+
 /* ---- introspection used by tests and the benchmark --------------------------------------- */
 
 /* Number of kernels this library has launched on the calling thread since the last reset. */

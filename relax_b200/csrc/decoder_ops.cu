@@ -1,0 +1,317 @@
+// Glue kernels of one Llama-style decode step around the quantised matmuls: RMSNorm (with the
+// residual add fused), rotary embedding + KV-cache append, single-query attention over the fp16
+// cache (split over the context, partials combined by a second kernel) and SwiGLU.
+//
+// The reference has no op for RMSNorm, RoPE or attention (its op list stops at mean / sqrt /
+// divide / multiply / strided_slice / concat / softmax / silu, python/tvm/relax/transform/
+// legalize_ops.py:378-381,506-514); the semantics here are the composition of those ops with
+// statistics in fp32 and one fp16 rounding at each kernel's output, which is what the oracle's
+// decoder restatement does too.
+//
+// All of them are HBM/latency bound and tiny next to the weight streams, except the attention,
+// which reads 2 * ctx * heads * 128 fp16 per sequence.
+#include "internal.h"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// y[b,:] = fp16( f32(x) * rsqrt(mean(f32(x)^2) + eps) * f32(w) ); optionally x += delta first (the
+// updated x is written back: it is the residual stream).  One CTA per row, H % 8 == 0.
+template <bool kAdd>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(__half* __restrict__ x, const __half* __restrict__ delta, const __half* __restrict__ w,
+               __half* __restrict__ y, int H, float eps) {
+  ptx::pdl_wait();
+  extern __shared__ float xs[];                 // H floats
+  __shared__ float red[8];
+  const int b = blockIdx.x;
+  __half* xr = x + (int64_t)b * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    __half2* h = reinterpret_cast<__half2*>(&v);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __half22float2(h[j]);
+      f[2 * j] = t.x;
+      f[2 * j + 1] = t.y;
+    }
+    if (kAdd) {
+      uint4 dv = *reinterpret_cast<const uint4*>(delta + (int64_t)b * H + i);
+      __half2* dh = reinterpret_cast<__half2*>(&dv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 t = __half22float2(dh[j]);
+        // the residual stream is stored in fp16: round the sum once, then normalise what was stored
+        __half2 r = __floats2half2_rn(f[2 * j] + t.x, f[2 * j + 1] + t.y);
+        h[j] = r;
+        float2 rf = __half22float2(r);
+        f[2 * j] = rf.x;
+        f[2 * j + 1] = rf.y;
+      }
+      *reinterpret_cast<uint4*>(xr + i) = v;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      xs[i + j] = f[j];
+      ss += f[j] * f[j];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)H + eps);
+  ptx::pdl_launch_dependents();
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+    const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 wf = __half22float2(wh[j]);
+      oh[j] = __floats2half2_rn(xs[i + 2 * j] * inv * wf.x, xs[i + 2 * j + 1] * inv * wf.y);
+    }
+    *reinterpret_cast<uint4*>(y + (int64_t)b * H + i) = o;
+  }
+}
+
+// Rotary embedding (rotate-half pairing i <-> i+64 inside a 128-wide head) of q and k, then k and v
+// go to the cache at position pos[0].  qkv row layout: [q heads | k heads | v heads], nh heads each.
+// cos/sin tables fp32 [max_pos, 64].  grid (nh, B), 64 threads.
+__global__ void __launch_bounds__(64)
+rope_kv_append_kernel(const __half* __restrict__ qkv, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                      const int* __restrict__ pos_ptr, __half* __restrict__ q_out, __half* __restrict__ k_cache,
+                      __half* __restrict__ v_cache, int nh, int max_ctx) {
+  ptx::pdl_wait();
+  const int h = blockIdx.x, b = blockIdx.y, i = threadIdx.x;
+  const int pos = pos_ptr[0];
+  const float c = cos_t[(int64_t)pos * 64 + i], s = sin_t[(int64_t)pos * 64 + i];
+  const __half* row = qkv + (int64_t)b * 3 * nh * 128;
+  const __half* q = row + h * 128;
+  const __half* k = row + (nh + h) * 128;
+  const __half* v = row + (2 * nh + h) * 128;
+  const float q0 = __half2float(q[i]), q1 = __half2float(q[i + 64]);
+  const float k0 = __half2float(k[i]), k1 = __half2float(k[i + 64]);
+  __half* qo = q_out + ((int64_t)b * nh + h) * 128;
+  qo[i] = __float2half_rn(q0 * c - q1 * s);
+  qo[i + 64] = __float2half_rn(q1 * c + q0 * s);
+  const int64_t slot = (((int64_t)b * max_ctx + pos) * nh + h) * 128;
+  k_cache[slot + i] = __float2half_rn(k0 * c - k1 * s);
+  k_cache[slot + i + 64] = __float2half_rn(k1 * c + k0 * s);
+  v_cache[slot + i] = v[i];
+  v_cache[slot + i + 64] = v[i + 64];
+  ptx::pdl_launch_dependents();
+}
+
+// Single-query attention, split over the context: CTA (split, head, batch) handles tokens
+// [split*chunk, min(ctx, (split+1)*chunk)) with an online softmax in fp32 and writes the partial
+// (max, sum, acc[128]) to scratch [B, nh, nsplit, 130] floats.  4 warps; lane owns 4 of the 128 dims.
+constexpr int kAttnChunk = 128;
+__global__ void __launch_bounds__(128)
+attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
+                           const __half* __restrict__ v_cache, const int* __restrict__ pos_ptr,
+                           float* __restrict__ scratch, int nh, int max_ctx, int nsplit, float scale_log2e) {
+  ptx::pdl_wait();
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int ctx = pos_ptr[0] + 1;
+  const int t0 = split * kAttnChunk;
+  const int t1 = min(ctx, t0 + kAttnChunk);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* out = scratch + (((int64_t)b * nh + h) * nsplit + split) * 130;
+  __shared__ float sm_m[4], sm_l[4], sm_acc[4][128];
+  float qf[4];
+  {
+    uint2 qv = *reinterpret_cast<const uint2*>(q + ((int64_t)b * nh + h) * 128 + lane * 4);
+    const __half2* qh = reinterpret_cast<const __half2*>(&qv);
+    float2 a = __half22float2(qh[0]), c = __half22float2(qh[1]);
+    qf[0] = a.x * scale_log2e; qf[1] = a.y * scale_log2e; qf[2] = c.x * scale_log2e; qf[3] = c.y * scale_log2e;
+  }
+  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int64_t tok_stride = (int64_t)nh * 128;
+  const __half* kb = k_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
+  const __half* vb = v_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
+  for (int t = t0 + warp; t < t1; t += 4) {
+    uint2 kv = *reinterpret_cast<const uint2*>(kb + t * tok_stride);
+    uint2 vv = *reinterpret_cast<const uint2*>(vb + t * tok_stride);
+    const __half2* kh = reinterpret_cast<const __half2*>(&kv);
+    float2 k01 = __half22float2(kh[0]), k23 = __half22float2(kh[1]);
+    float s = qf[0] * k01.x + qf[1] * k01.y + qf[2] * k23.x + qf[3] * k23.y;
+    s = warp_sum(s);                                 // log2-domain score
+    const float mn = fmaxf(m, s);
+    const float corr = exp2f(m - mn), p = exp2f(s - mn);
+    const __half2* vh = reinterpret_cast<const __half2*>(&vv);
+    float2 v01 = __half22float2(vh[0]), v23 = __half22float2(vh[1]);
+    l = l * corr + p;
+    acc[0] = acc[0] * corr + p * v01.x;
+    acc[1] = acc[1] * corr + p * v01.y;
+    acc[2] = acc[2] * corr + p * v23.x;
+    acc[3] = acc[3] * corr + p * v23.y;
+    m = mn;
+  }
+  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) sm_acc[warp][lane * 4 + j] = acc[j];
+  __syncthreads();
+  ptx::pdl_launch_dependents();
+  // combine the 4 warps: thread d owns output dim d
+  const int d = threadIdx.x;
+  float M = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+  float L = 0.f, A = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const float f = (sm_m[w] == -INFINITY) ? 0.f : exp2f(sm_m[w] - M);
+    L += sm_l[w] * f;
+    A += sm_acc[w][d] * f;
+  }
+  out[2 + d] = A;
+  if (d == 0) { out[0] = M; out[1] = L; }
+}
+
+// Merges the nsplit partials of one (batch, head) and writes fp16 [B, nh*128].  grid (nh, B), 128 threads.
+__global__ void __launch_bounds__(128)
+attn_decode_combine_kernel(const float* __restrict__ scratch, const int* __restrict__ pos_ptr, __half* __restrict__ out,
+                           int nh, int nsplit) {
+  ptx::pdl_wait();
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int ctx = pos_ptr[0] + 1;
+  const int used = (ctx + kAttnChunk - 1) / kAttnChunk;
+  const float* p = scratch + ((int64_t)b * nh + h) * nsplit * 130;
+  float M = -INFINITY;
+  for (int s = 0; s < used; ++s) M = fmaxf(M, p[s * 130]);
+  float L = 0.f, A = 0.f;
+  for (int s = 0; s < used; ++s) {
+    const float f = exp2f(p[s * 130] - M);
+    L += p[s * 130 + 1] * f;
+    A += p[s * 130 + 2 + d] * f;
+  }
+  ptx::pdl_launch_dependents();
+  out[((int64_t)b * nh + h) * 128 + d] = __float2half_rn(A / L);
+}
+
+// out[b,i] = fp16( silu(f32(g)) * f32(u) ), gu row = [gate (I) | up (I)].  I % 8 == 0.
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ out, int I, int64_t total8) {
+  ptx::pdl_wait();
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const int per_row = I / 8;
+  const int64_t b = idx / per_row;
+  const int i = (int)(idx - b * per_row) * 8;
+  uint4 gv = *reinterpret_cast<const uint4*>(gu + b * 2 * I + i);
+  uint4 uv = *reinterpret_cast<const uint4*>(gu + b * 2 * I + I + i);
+  const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+  const __half2* uh = reinterpret_cast<const __half2*>(&uv);
+  uint4 o;
+  __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 g = __half22float2(gh[j]), u = __half22float2(uh[j]);
+    float a = g.x / (1.f + __expf(-g.x)) * u.x;
+    float c = g.y / (1.f + __expf(-g.y)) * u.y;
+    oh[j] = __floats2half2_rn(a, c);
+  }
+  ptx::pdl_launch_dependents();
+  *reinterpret_cast<uint4*>(out + b * I + i) = o;
+}
+
+template <typename K, typename... A>
+int launch(const char* what, K kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = options().gemv_pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
+  if (e != cudaSuccess) return fail(B200_ELAUNCH, "%s launch: %s", what, cudaGetErrorString(e));
+  count_launch();
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_rmsnorm(void* x, const void* delta, const void* w, void* y, int64_t B, int64_t H, float eps, void* stream) {
+  if (B < 0 || H <= 0 || H % 8 != 0 || H > 16384) return fail(B200_EINVAL, "rmsnorm: need 0 < H <= 16384, H %% 8 == 0");
+  if (B == 0) return B200_OK;
+  if (!x || !w || !y) return fail(B200_EINVAL, "rmsnorm: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  auto s = static_cast<cudaStream_t>(stream);
+  if (delta)
+    return launch("add_rmsnorm", rmsnorm_kernel<true>, dim3((unsigned)B), dim3(256), (size_t)H * 4, s, (__half*)x,
+                  (const __half*)delta, (const __half*)w, (__half*)y, (int)H, eps);
+  return launch("rmsnorm", rmsnorm_kernel<false>, dim3((unsigned)B), dim3(256), (size_t)H * 4, s, (__half*)x,
+                (const __half*)nullptr, (const __half*)w, (__half*)y, (int)H, eps);
+}
+
+int b200_rope_kv_append(const void* qkv, const void* cos_t, const void* sin_t, const void* pos, void* q_out,
+                        void* k_cache, void* v_cache, int64_t B, int64_t nh, int64_t max_ctx, void* stream) {
+  if (B <= 0 || nh <= 0 || max_ctx <= 0) return fail(B200_EINVAL, "rope_kv_append: bad sizes");
+  if (!qkv || !cos_t || !sin_t || !pos || !q_out || !k_cache || !v_cache) return fail(B200_EINVAL, "rope_kv_append: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  return launch("rope_kv_append", rope_kv_append_kernel, dim3((unsigned)nh, (unsigned)B), dim3(64), 0,
+                static_cast<cudaStream_t>(stream), (const __half*)qkv, (const float*)cos_t, (const float*)sin_t,
+                (const int*)pos, (__half*)q_out, (__half*)k_cache, (__half*)v_cache, (int)nh, (int)max_ctx);
+}
+
+int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t max_ctx) {
+  int64_t nsplit = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+  return B * nh * nsplit * 130 * (int64_t)sizeof(float);
+}
+
+int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out, void* scratch,
+                     int64_t B, int64_t nh, int64_t max_ctx, void* stream) {
+  if (B <= 0 || nh <= 0 || max_ctx <= 0) return fail(B200_EINVAL, "attn_decode: bad sizes");
+  if (!q || !k_cache || !v_cache || !pos || !out || !scratch) return fail(B200_EINVAL, "attn_decode: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  const int nsplit = (int)((max_ctx + kAttnChunk - 1) / kAttnChunk);
+  auto s = static_cast<cudaStream_t>(stream);
+  const float scale_log2e = 1.4426950408889634f / sqrtf(128.f);
+  rc = launch("attn_decode_partial", attn_decode_partial_kernel, dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B),
+              dim3(128), 0, s, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, (const int*)pos,
+              (float*)scratch, (int)nh, (int)max_ctx, nsplit, scale_log2e);
+  if (rc) return rc;
+  return launch("attn_decode_combine", attn_decode_combine_kernel, dim3((unsigned)nh, (unsigned)B), dim3(128), 0, s,
+                (const float*)scratch, (const int*)pos, (__half*)out, (int)nh, nsplit);
+}
+
+int b200_silu_mul(const void* gu, void* out, int64_t B, int64_t I, void* stream) {
+  if (B < 0 || I <= 0 || I % 8 != 0) return fail(B200_EINVAL, "silu_mul: need I %% 8 == 0");
+  if (B == 0) return B200_OK;
+  if (!gu || !out) return fail(B200_EINVAL, "silu_mul: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  const int64_t total8 = B * (I / 8);
+  return launch("silu_mul", silu_mul_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0,
+                static_cast<cudaStream_t>(stream), (const __half*)gu, (__half*)out, (int)I, total8);
+}
+
+}  // extern "C"
