@@ -17,6 +17,7 @@ q4f16_dequantize_kernel(const uint32_t* __restrict__ wq, const __half* __restric
                         uint4* __restrict__ w, int64_t n_words, int words_per_row) {
   // words_per_row = K/8; a group of 32 k is 4 consecutive words, and rows hold a whole number
   // of groups, so scale index = word index / 4.
+  const Q4Consts qc = q4_consts();
   int64_t base = (int64_t)blockIdx.x * (kDeqThreads * kDeqUnroll) + threadIdx.x;
   uint32_t word[kDeqUnroll];
   __half sc[kDeqUnroll];
@@ -30,7 +31,7 @@ q4f16_dequantize_kernel(const uint32_t* __restrict__ wq, const __half* __restric
 #pragma unroll
   for (int u = 0; u < kDeqUnroll; ++u) {
     int64_t i = base + (int64_t)u * kDeqThreads;
-    if (i < n_words) w[i] = q4_dequant_natural(word[u], __half2(sc[u], sc[u]));
+    if (i < n_words) w[i] = q4_dequant_natural(word[u], __half2(sc[u], sc[u]), qc);
   }
   (void)words_per_row;
 }

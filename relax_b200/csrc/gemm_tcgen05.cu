@@ -241,6 +241,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ dequantisers
     const int r = tid - 256;                        // weight row inside the tile, 0..255
     const int r8 = r & 7;
+    const Q4Consts qc = q4_consts();
     uint32_t it_raw = 0, it_sc = 0, it_b = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int tn = tile / p.tiles_m;
@@ -303,7 +304,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const uint4 o = q4_dequant_natural(words[c], c < 4 ? s_lo : s_hi);
+          const uint4 o = q4_dequant_natural(words[c], c < 4 ? s_lo : s_hi, qc);
           *reinterpret_cast<uint4*>(brow + ((c ^ r8) << 4)) = o;
         }
         fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's async proxy

@@ -73,6 +73,7 @@ q4f16_gemv_stream_kernel(const __half* __restrict__ x, const uint32_t* __restric
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* xs = reinterpret_cast<uint4*>(smem_raw);  // [kblk/8 words][NC] permuted x
 
+  const Q4Consts qc = q4_consts();
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -186,8 +187,8 @@ q4f16_gemv_stream_kernel(const __half* __restrict__ x, const uint32_t* __restric
             const uint4& w1 = cur.w[rt][1][u];
             uint32_t word0 = wd == 0 ? w0.x : wd == 1 ? w0.y : wd == 2 ? w0.z : w0.w;
             uint32_t word1 = wd == 0 ? w1.x : wd == 1 ? w1.y : wd == 2 ? w1.z : w1.w;
-            q4_dequant_pairs(word0, cur.s[rt][0][u], a_lo);
-            q4_dequant_pairs(word1, cur.s[rt][1][u], a_hi);
+            q4_dequant_pairs(word0, cur.s[rt][0][u], a_lo, qc);
+            q4_dequant_pairs(word1, cur.s[rt][1][u], a_hi, qc);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               mma_16x8x16(acc[rt][mt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[mt].x, b[mt].y);

@@ -1,34 +1,36 @@
-// Skinny q4f16 matmul, pipelined form: persistent CTAs fed by TMA.
+// Skinny q4f16 matmul, pipelined form: CTAs fed by TMA.
 //
 // The register-streaming kernel in gemv.cu can keep only a couple of KB per warp in flight,
-// far short of the ~40 KB per SM that HBM3e needs to stay busy, and many small bulk copies are
-// bound by the TMA unit's per-instruction cost (measured here: one issuing thread sustains
-// about 2.2 tiled loads per microsecond whatever their size, so a load must carry ~32 KB).
-// Two producer threads per CTA each issue one tiled TMA load per stage (32 KB of packed
-// weights; 4 KB of scales) into a ring of shared-memory stages (~140 KB in flight per CTA)
-// and eight consumer warps drain it:
+// far short of the ~40 KB per SM that HBM3e needs to stay busy.  Here two producer threads per
+// CTA each issue one tiled TMA load per stage (packed weights; scales) into a ring of
+// shared-memory stages and CW consumer warps drain it:
 //
-//   stage      = 16 rows of W x 4096 k.  The weights are seen through a 3-D tensor map
-//                (32 words = 256 k | row | 256-k chunk) so that one box {32,16,16} lands as
+//   stage      = 16 rows of W x CH chunks of 256 k.  The weights are seen through a 3-D tensor
+//                map (32 words = 256 k | row | 256-k chunk) so that one box {32,16,CH} lands as
 //                [chunk][row][128 B] with the 128-byte swizzle: the eight rows a warp reads in
 //                one instruction then sit in eight different bank groups.  The scales use the
-//                same trick with 16-byte units ([unit of 8 groups][row][16 B]).  Rows past N and
-//                chunks past K are zero-filled by the TMA unit (zero scale => zero weight).
-//   consumer w = lane (g,t) owns, for rows g and g+8, the 16-byte words (= scale groups) 2t+(w&1)
-//                of chunks w/2 + 4j; it dequantises them (exact q-7, one HMUL2 by the scale, as
-//                the reference rounds) and feeds mma.sync m16n8k16 with x fragments read from
-//                a copy of x kept in shared memory in the matching permuted order
-//   row tile   = 16 rows over the whole K range; partial sums of the 8 warps meet in shared
-//                memory (double-buffered, one named barrier per tile) and are stored as fp16
-//   CTA        = persistent: row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+//                same trick with 16-byte units ([chunk][row][8 scales]).  Rows past N and chunks
+//                past K are zero-filled by the TMA unit (zero scale => zero weight).
+//   consumer w = takes chunks w, w + CW, ... of a stage.  Lane (g,t) owns, for rows g and g+8,
+//                the scale groups 2t and 2t+1 of the chunk (two 16-byte words per row and one
+//                32-bit pair of scales per row); it copies them to registers, hands the stage
+//                back, dequantises (exact q-7, one HMUL2 by the scale, as the reference rounds)
+//                and feeds mma.sync m16n8k16 with x fragments read from a copy of x kept in
+//                shared memory in the matching permuted order.
+//   row tile   = 16 rows over the whole K range; each warp leaves its partial sums in shared
+//                memory and bumps a counter; the warp that arrives last adds them up (in warp
+//                order, so the result does not depend on who is last) and stores fp16.  Nobody
+//                waits at a tile boundary, so the warps drift apart and the shared-memory loads
+//                of one overlap the arithmetic of another.
+//   CTA        = row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 //
 // When x does not fit beside the ring (large M*K) the K range is cut into blocks: x is restaged
 // per block and per-tile partial sums are carried in a small shared-memory array.
 //
 // Programmatic dependent launch: the weights never depend on the previous kernel in the stream,
 // so the producer starts copying before griddepcontrol.wait; only the consumers (which read x
-// and write y) wait.  At ~110 KB of shared memory two consecutive launches fit on one SM, which
-// hides the fill/drain bubble between back-to-back decode matmuls when shared memory allows.
+// and write y) wait.  Several CTAs fit on one SM, so the CTAs of the next launch move in as
+// those of the previous one leave and their first copies are in flight while it drains.
 //
 // Requires K % 256 == 0 and 16-byte aligned scales (tensor-map stride rules); other shapes use
 // the register-streaming kernel.
@@ -45,15 +47,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 2) * 32;   // + one producer warp for weights, one for scales
-constexpr int kChunks = 16;              // 256-k chunks per stage
-constexpr int KC = 256 * kChunks;        // k per stage (4096)
 constexpr int kRows = 16;                // rows per stage / row tile
-constexpr int kWBytes = kChunks * kRows * 128;      // 32768: [chunk][row][128 B], 128B-swizzled
-constexpr int kSBytes = kRows * (KC / 32) * 2;      // 4096:  [unit = chunk][row][8 scales = 16 B]
-constexpr int kStageBytes = kWBytes + kSBytes;      // 36864 (a multiple of 1024, as the swizzle needs)
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 8;
 constexpr uint64_t kConsumerWaitNs = 2000000000ull;     // 2 s: a stage copy takes microseconds
 constexpr uint64_t kProducerWaitNs = 30000000000ull;    // 30 s: may span the previous kernel's whole run
 
@@ -65,33 +60,30 @@ __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Layout of the staged x block: one 16-byte slot per (8-k word jw, batch column).  The four
-// lanes t of a row-group read words 8 apart in the same instruction, so the slot index must
-// differ mod 8 between them:
+// Layout of the staged x block: one 16-byte slot per (8-k word jw, batch column).  Lane (g,t)
+// reads column g of words 32c + 8t + i (i = 0..7), so the four lanes t of a row-group read
+// words 8 apart in the same instruction and their slots must differ mod 8:
 //   NC >= 8: NC slots per word, column XOR-ed with 2*((jw>>3)&3)  (= 2t);
-//   NC <  8: NC+1 slots per word -- the extra column stays zero and is what lanes whose batch
-//            column does not exist read, so the load needs no predicate -- plus 2 slots of padding
-//            after every 8 words.
+//   NC <  8: NC slots per word plus NC slots of padding after every 8 words.
 template <int NC>
 struct XLayout {
-  static constexpr int kSlotsPerWord = NC >= 8 ? NC : NC + 1;
   __device__ __forceinline__ static int slot(int jw, int col) {
     if (NC >= 8) return jw * NC + (col ^ (((jw >> 3) & 3) << 1));
-    return jw * kSlotsPerWord + col + 2 * (jw >> 3);
+    return NC * (jw + (jw >> 3)) + col;
   }
-  // bytes for a block of `k` (multiple of 64)
-  __host__ __device__ static constexpr size_t bytes(int k) {
-    return NC >= 8 ? (size_t)NC * k * 2 : ((size_t)(k / 8) * kSlotsPerWord + 2 * (size_t)(k / 64)) * 16;
-  }
+  // slots per 256-k chunk (32 words)
+  static constexpr int kSlotsPerChunk = NC >= 8 ? 32 * NC : 36 * NC;
+  // bytes for a block of `k` (multiple of 256)
+  __host__ __device__ static constexpr size_t bytes(int k) { return (size_t)(k / 256) * kSlotsPerChunk * 16; }
 };
 
 struct PipeParams {
-  CUtensorMap tm_w;   // uint32 {32, N, K/256}, box {32, 16, 16}, 128B swizzle
-  CUtensorMap tm_s;   // fp16   {8, N, K/256},  box {8, 16, 16}
+  CUtensorMap tm_w;   // uint32 {32, N, K/256}, box {32, 16, CH}, 128B swizzle
+  CUtensorMap tm_s;   // fp16   {8, N, K/256},  box {8, 16, CH}
   const __half* x;
   __half* y;
   int M, N, K;
-  int kblk;        // k per x block (multiple of KC, or >= K)
+  int kblk;        // k per x block (multiple of the stage's k, or >= K)
   int nstages;
   int ntiles;      // ceil(N / 16)
   int tiles_per_cta;
@@ -100,14 +92,23 @@ struct PipeParams {
 // Shared memory carve-up (after rounding the base up to 1024 bytes):
 //   ring: nstages * kStageBytes
 //   [.., +8*2*kMaxStages)          full / empty mbarriers
-//   xs:   NC * kblk * 2            permuted x block
-//   red:  2 * 8 * MT*128 * 4       cross-warp partial sums, double buffered
+//   xs:   XLayout::bytes(kblk)     permuted x block
+//   red:  (nstages+1) * CW * MT*128 * 4   cross-warp partial sums; a warp is never more than
+//                                  nstages tiles ahead of the slowest one (stage hand-back needs all)
+//   cnt:  (nstages+1) ints         warps arrived per buffer
 //   accs: tiles_per_cta * MT*128*4 (only when K is cut into several blocks)
-template <int NC>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int NC, int CW, int CH, int DBG = 0>
+__global__ void __launch_bounds__((CW + 2) * 32, 1)
 q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   constexpr int MT = (NC + 7) / 8;
   constexpr int kOut = MT * 128;           // outputs per row tile held in fragment order
+  constexpr int KC = 256 * CH;             // k per stage
+  constexpr int kWBytes = CH * kRows * 128;           // [chunk][row][128 B], 128B-swizzled
+  constexpr int kSBytes = CH * kRows * 16;            // [chunk][row][8 scales = 16 B]
+  constexpr int kStageBytes = kWBytes + kSBytes;      // a multiple of 1024, as the swizzle needs
+  constexpr int U = CH / CW;                          // chunks per warp per stage
+  static_assert(CH % CW == 0 && U >= 1, "each consumer warp takes whole chunks");
+  static_assert(kStageBytes % 1024 == 0, "stage alignment");
   extern __shared__ unsigned char smem_unaligned[];
   // Round the base up to 1024 bytes by OFFSETTING the shared array (not by casting through an
   // integer): the compiler then still knows these are shared-memory addresses and emits LDS/STS.
@@ -116,7 +117,9 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   uint64_t* empty = full + kMaxStages;
   uint4* xs = reinterpret_cast<uint4*>(empty + kMaxStages);
   float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + XLayout<NC>::bytes(p.kblk));
-  float* accs = red + 2 * kConsumerWarps * kOut;
+  const int nred = p.nstages + 1;
+  int* cnt = reinterpret_cast<int*>(red + nred * CW * kOut);
+  float* accs = reinterpret_cast<float*>(cnt + kMaxStages + 1);
 
   __shared__ int s_abort;                    // set once a bounded wait gives up: later waits are skipped
 
@@ -127,31 +130,32 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
 
   if (tid == 0) {
     s_abort = 0;
+    for (int s = 0; s <= kMaxStages; ++s) cnt[s] = 0;
     for (int s = 0; s < p.nstages; ++s) {
       mbar_init(&full[s], 2);
-      mbar_init(&empty[s], kConsumerWarps);
+      mbar_init(&empty[s], CW);
     }
     mbar_fence_init();
   }
   __syncthreads();
   pdl_launch_dependents();
 
-  if (warp >= kConsumerWarps) {
+  if (warp >= CW) {
     // ------------------------------------------------------------------ producer warps
-    // warp 8 loads the packed weights, warp 9 the scales: one tiled load per stage each.
-    const bool is_w = warp == kConsumerWarps;
+    // warp CW loads the packed weights, warp CW+1 the scales: one tiled load per stage each.
+    const bool is_w = warp == CW;
     if (lane == 0) {
       prefetch_tmap(is_w ? &p.tm_w : &p.tm_s);
       const uint64_t policy = policy_evict_first();
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t round = 0;              // how many times the ring has wrapped
       for (int kb = 0; kb < nkb; ++kb) {
         const int k_lo = kb * p.kblk;
         const int k_hi = min(p.K, k_lo + p.kblk);
         for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
           const int row0 = tile * kRows;
-          for (int k0 = k_lo; k0 < k_hi; k0 += KC, ++it) {
-            const int s = it % p.nstages;
-            const uint32_t round = it / p.nstages;
+          for (int k0 = k_lo; k0 < k_hi; k0 += KC, s = (s + 1 == p.nstages ? 0 : s + 1), round += (s == 0)) {
+            if (DBG >= 4 && round > 0) continue;
             if (round > 0) {
               // Legitimately as long as the previous kernel in the stream runs (the consumers
               // that free the stages sit in griddepcontrol.wait until then): bound it by time.
@@ -180,13 +184,26 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   // -------------------------------------------------------------------- consumer warps
   const int g = lane >> 2;
   const int t = lane & 3;
-  const int ctid = tid;                          // 0..255
-  constexpr int kConsumers = kConsumerWarps * 32;
+  constexpr int kConsumers = CW * 32;
 
+  // Per-thread offsets inside a stage (chunk `warp`; further chunks of this warp are CW chunks on).
+  //   weights: row g at (chunk*16 + g)*128, 16-byte word j at ((j ^ g) << 4); row g+8 is 1024 on
+  //   (same swizzle phase).  Words 2t and 2t+1 differ in bit 4 only.
+  const uint32_t w_off = (uint32_t)((warp * kRows + g) * 128 + (((2 * t) ^ g) << 4));
+  const uint32_t s_off = (uint32_t)(kWBytes + (warp * kRows + g) * 16 + t * 4);
+  // x: words 32*chunk + 8t + i of the staged block, column g (the k-block offset is added per stage)
+  // Lanes whose batch column does not exist (g >= NC) read column 0: what they feed into the MMA
+  // only reaches output columns >= NC, which are never stored.
+  const uint4* x_thr = xs + (NC >= 8 ? (warp * 32 + 8 * t) * NC + (g ^ (2 * t)) : NC * (warp * 36 + 9 * t) + (g < NC ? g : 0));
+  constexpr int kXStage = CH * XLayout<NC>::kSlotsPerChunk;   // slots per stage
+  constexpr int kXUnit = CW * XLayout<NC>::kSlotsPerChunk;    // slots between this warp's chunks
+
+  const Q4Consts qc = q4_consts();
   pdl_wait();                                    // x may be the previous kernel's output
 
-  uint32_t it = 0;
-  uint32_t tile_parity = 0;
+  int s = 0;                                     // ring slot of the current stage
+  uint32_t round = 0;                            // how many times the ring has wrapped
+  int rb = 0;                                    // reduction buffer of the current tile
   for (int kb = 0; kb < nkb; ++kb) {
     const int k_lo = kb * p.kblk;
     const int k_hi = min(p.K, k_lo + p.kblk);
@@ -194,9 +211,8 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     if (kb > 0) bar_sync(1, kConsumers);         // everyone is done reading the previous block
     {
       const int words = p.kblk >> 3;
-      constexpr int SPW = XLayout<NC>::kSlotsPerWord;
-      for (int i = ctid; i < words * SPW; i += kConsumers) {
-        int j = i / SPW, m = i - j * SPW;
+      for (int i = tid; i < words * NC; i += kConsumers) {
+        int j = i / NC, m = i - j * NC;
         int k = k_lo + j * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (m < p.M && k < p.K) v = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
@@ -220,59 +236,77 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
 
-      for (int k0 = k_lo; k0 < k_hi; k0 += KC, ++it) {
-        const int s = it % p.nstages;
-        const uint32_t round = it / p.nstages;
+      const uint4* xk = x_thr;
+      for (int k0 = k_lo; k0 < k_hi; k0 += KC, xk += kXStage, s = (s + 1 == p.nstages ? 0 : s + 1), round += (s == 0)) {
         // On a timeout the kernel keeps going without waiting (results are garbage, the error
         // flag says so) so that every warp still reaches the named barriers and the CTA ends.
-        if (!*(volatile int*)&s_abort && !mbar_wait_ns(&full[s], round & 1, kConsumerWaitNs)) {
-          atomicExch(&g_gemv_pipe_error, 2);
-          *(volatile int*)&s_abort = 1;
+        if ((DBG < 4 || round == 0) && !mbar_try_wait(&full[s], round & 1)) {
+          if (!*(volatile int*)&s_abort && !mbar_wait_ns(&full[s], round & 1, kConsumerWaitNs)) {
+            atomicExch(&g_gemv_pipe_error, 2);
+            *(volatile int*)&s_abort = 1;
+          }
         }
         const unsigned char* st = ring + (size_t)s * kStageBytes;
-        const int u = 2 * t + (warp & 1);                     // 16-byte word (= group) inside a 256-k chunk
-        const int swz = (u ^ g) << 4;                         // 128B swizzle: word index XOR (row % 8)
+        uint4 w[U][2][2];        // [chunk of this warp][row g / g+8][group 2t / 2t+1]
+        uint32_t sc[U][2];       // scales of groups (2t, 2t+1) as a half2, rows g / g+8
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint4 w0[2], w1[2];
-          __half sc0[2], sc1[2];
+        for (int u = 0; u < U; ++u) {
+          const unsigned char* su = st + u * (CW * kRows * 128);
+          w[u][0][0] = *reinterpret_cast<const uint4*>(su + w_off);
+          w[u][0][1] = *reinterpret_cast<const uint4*>(su + (w_off ^ 16u));
+          w[u][1][0] = *reinterpret_cast<const uint4*>(su + w_off + 1024);
+          w[u][1][1] = *reinterpret_cast<const uint4*>(su + (w_off ^ 16u) + 1024);
+          const unsigned char* ss = st + u * (CW * kRows * 16);
+          sc[u][0] = *reinterpret_cast<const uint32_t*>(ss + s_off);
+          sc[u][1] = *reinterpret_cast<const uint32_t*>(ss + s_off + 128);
+        }
+        // the loads must have returned before the stage goes back to the producer
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int c = (warp >> 1) + 4 * (2 * half + j);   // chunk inside the stage
-            w0[j] = *reinterpret_cast<const uint4*>(st + (c * kRows + g) * 128 + swz);
-            w1[j] = *reinterpret_cast<const uint4*>(st + (c * kRows + g + 8) * 128 + swz);
-            // scales: [chunk c][row][8 groups]; this thread's group is number u of the chunk
-            sc0[j] = *reinterpret_cast<const __half*>(st + kWBytes + (c * kRows + g) * 16 + u * 2);
-            sc1[j] = *reinterpret_cast<const __half*>(st + kWBytes + (c * kRows + g + 8) * 16 + u * 2);
-          }
-          if (half == 1) {
-            // the loads must have returned before the stage goes back to the producer
+        for (int u = 0; u < U; ++u) {
+          pin_loaded(w[u][0][0]);
+          pin_loaded(w[u][0][1]);
+          pin_loaded(w[u][1][0]);
+          pin_loaded(w[u][1][1]);
+          pin_loaded(sc[u][0]);
+          pin_loaded(sc[u][1]);
+        }
+        if (DBG != 6 && DBG != 7) fence_proxy_async_smem();   // generic reads ordered before the TMA refill (async proxy)
+        if (DBG != 7) __syncwarp();
+        if (DBG != 7 && lane == 0) mbar_arrive(&empty[s]);            // all of this warp's share is in registers
+
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              pin_loaded(w0[j]);
-              pin_loaded(w1[j]);
-              pin_loaded((uint32_t)__half_as_ushort(sc0[j]) | ((uint32_t)__half_as_ushort(sc1[j]) << 16));
-            }
-            fence_proxy_async_smem();   // generic reads ordered before the TMA refill (async proxy)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);            // all of the stage is in registers: hand it back
-          }
+        for (int u = 0; u < U; ++u) {
+          // chunks past K were zero-filled: nothing to add
+          if (k0 + (warp + u * CW) * 256 >= k_hi) continue;
+          const uint4* xu = xk + u * kXUnit;
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int gl = ((warp >> 1) + 4 * (2 * half + j)) * 8 + u;   // group inside the stage
-            const __half2 s0 = __half2(sc0[j], sc0[j]), s1 = __half2(sc1[j], sc1[j]);
-            const int jbase = (((k0 - k_lo) >> 5) + gl) * 4;  // word index inside the staged x block
-            const uint32_t wr0[4] = {w0[j].x, w0[j].y, w0[j].z, w0[j].w};
-            const uint32_t wr1[4] = {w1[j].x, w1[j].y, w1[j].z, w1[j].w};
-            const uint4* xb = xs + XLayout<NC>::slot(jbase, NC >= 8 ? g : (g < NC ? g : NC));
+          for (int h = 0; h < 2; ++h) {
+            const __half2 sp0 = u32_as_h2(sc[u][0]), sp1 = u32_as_h2(sc[u][1]);
+            const __half2 s0 = h ? __high2half2(sp0) : __low2half2(sp0);
+            const __half2 s1 = h ? __high2half2(sp1) : __low2half2(sp1);
+            const uint32_t wr0[4] = {w[u][0][h].x, w[u][0][h].y, w[u][0][h].z, w[u][0][h].w};
+            const uint32_t wr1[4] = {w[u][1][h].x, w[u][1][h].y, w[u][1][h].z, w[u][1][h].w};
 #pragma unroll
             for (int wd = 0; wd < 4; ++wd) {
               uint4 b[MT];
 #pragma unroll
-              for (int mt = 0; mt < MT; ++mt) b[mt] = xb[wd * XLayout<NC>::kSlotsPerWord + 8 * mt];
+              for (int mt = 0; mt < MT; ++mt) b[mt] = xu[(4 * h + wd) * NC + 8 * mt];
               uint32_t a_lo[4], a_hi[4];
-              q4_dequant_pairs(wr0[wd], s0, a_lo);
-              q4_dequant_pairs(wr1[wd], s1, a_hi);
+              if (DBG == 1) {
+                acc[0][0][0] += __uint_as_float((wr0[wd] ^ wr1[wd] ^ b[0].x ^ h2_as_u32(s0) ^ h2_as_u32(s1)) & 0x007fffffu);
+                continue;
+              }
+              if (DBG == 2) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { a_lo[i] = wr0[wd] + i + h2_as_u32(s0); a_hi[i] = wr1[wd] - i + h2_as_u32(s1); }
+              } else {
+                q4_dequant_pairs(wr0[wd], s0, a_lo, qc);
+                q4_dequant_pairs(wr1[wd], s1, a_hi, qc);
+              }
+              if (DBG == 3) {
+                acc[0][0][0] += __uint_as_float((a_lo[0] ^ a_lo[1] ^ a_lo[2] ^ a_lo[3] ^ a_hi[0] ^ a_hi[1] ^ a_hi[2] ^ a_hi[3] ^ b[0].x) & 0x007fffffu);
+                continue;
+              }
 #pragma unroll
               for (int mt = 0; mt < MT; ++mt) {
                 mma_16x8x16(acc[0][mt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[mt].x, b[mt].y);
@@ -283,31 +317,41 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         }
       }
 
-      // ---- cross-warp reduction of this (tile, k block) ---------------------------------------------
-      float* rbuf = red + tile_parity * (kConsumerWarps * kOut);
-      tile_parity ^= 1;
+      // ---- cross-warp reduction of this (tile, k block): the last warp to arrive does it ---------------
+      float* rbuf = red + rb * (CW * kOut);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) rbuf[warp * kOut + (mt * 4 + i) * 32 + lane] = acc[0][mt][i] + acc[1][mt][i];
-      bar_sync(2, kConsumers);
-      if (ctid < kOut) {
-        float sum = 0.f;
+      __threadfence_block();
+      __syncwarp();
+      int arrived = 0;
+      if (lane == 0) arrived = atomicAdd(&cnt[rb], 1);
+      arrived = __shfl_sync(0xffffffffu, arrived, 0);
+      if (arrived == CW - 1) {
+        __threadfence_block();
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) sum += rbuf[w * kOut + ctid];
-        if (nkb > 1) {
-          float* a = accs + slot * kOut + ctid;
-          if (kb > 0) sum += *a;
-          if (kb < nkb - 1) *a = sum;
+        for (int q = 0; q < 4 * MT; ++q) {
+          const int e = q * 32 + lane;
+          float sum = 0.f;
+#pragma unroll
+          for (int w2 = 0; w2 < CW; ++w2) sum += rbuf[w2 * kOut + e];
+          if (nkb > 1) {
+            float* a = accs + slot * kOut + e;
+            if (kb > 0) sum += *a;
+            if (kb < nkb - 1) *a = sum;
+          }
+          if (kb == nkb - 1) {
+            const int i = q & 3, mt = q >> 2;
+            const int row = tile * kRows + (lane >> 2) + 8 * (i >> 1);
+            const int col = mt * 8 + 2 * (lane & 3) + (i & 1);
+            if (row < p.N && col < p.M) p.y[(int64_t)col * p.N + row] = __float2half_rn(sum);
+          }
         }
-        if (kb == nkb - 1) {
-          const int ln = ctid & 31, q = ctid >> 5;
-          const int i = q & 3, mt = q >> 2;
-          const int row = tile * kRows + (ln >> 2) + 8 * (i >> 1);
-          const int col = mt * 8 + 2 * (ln & 3) + (i & 1);
-          if (row < p.N && col < p.M) p.y[(int64_t)col * p.N + row] = __float2half_rn(sum);
-        }
+        __syncwarp();
+        if (lane == 0) cnt[rb] = 0;              // the buffer comes round again nstages+1 tiles later
       }
+      rb = rb + 1 == nred ? 0 : rb + 1;
     }
   }
   if (*(volatile int*)&s_abort) {
@@ -317,51 +361,63 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   }
 }
 
-template <int NC>
+template <int NC, int CW, int CH, int DBG = 0>
 int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int M, int N, int K,
                 cudaStream_t stream) {
   constexpr int MT = (NC + 7) / 8;
   constexpr int kOut = MT * 128;
+  constexpr int KC = 256 * CH;
+  constexpr int kStageBytes = CH * kRows * (128 + 16);
+  constexpr int kThreads = (CW + 2) * 32;
   PipeParams p;
   {
     const uint64_t wd[3] = {32, (uint64_t)N, (uint64_t)(K / 256)};
     const uint64_t ws[2] = {(uint64_t)K / 2, 128};
-    const uint32_t wb[3] = {32, kRows, kChunks};
+    const uint32_t wb[3] = {32, kRows, CH};
     int rc = make_tmap(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, wq, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     const uint64_t sd[3] = {8, (uint64_t)N, (uint64_t)(K / 256)};
     const uint64_t ss[2] = {(uint64_t)(K / 32) * 2, 16};
-    const uint32_t sb[3] = {8, kRows, kChunks};
+    const uint32_t sb[3] = {8, kRows, CH};
     rc = make_tmap(&p.tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, scales, sd, ss, sb, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
   }
   p.x = x; p.y = y;
   p.M = M; p.N = N; p.K = K;
   p.ntiles = (N + kRows - 1) / kRows;
-  int stages = (int)options().gemv_stages;
-  if (stages <= 0) stages = 2;
-  if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) stages = 2;
-  const size_t kMaxSmem = 227 * 1024;
   const int kpad = ((K + KC - 1) / KC) * KC;
+  const int stages_per_tile = kpad / KC;
+  int stages = (int)options().gemv_stages;
+  if (stages <= 0) stages = stages_per_tile >= 2 ? 2 : 1;   // registers are the extra buffer: a shallow ring is enough
+  if (stages > kMaxStages) stages = kMaxStages;
+  const size_t kMaxSmem = 227 * 1024;
+  const size_t kSmPool = 228 * 1024;   // shared memory per SM, 1 KB of it reserved per resident CTA
   const int sms = sm_count();
+  int max_per_sm = (int)options().gemv_ctas_per_sm;
+  if (max_per_sm <= 0) max_per_sm = 4;
+  const int by_threads = 2048 / kThreads;
+  if (max_per_sm > by_threads) max_per_sm = by_threads;
   size_t need = 0;
   int kblk = 0, grid = 0;
-  // Prefer a deep ring with the whole of x beside it; give up ring depth before cutting K into
-  // blocks (a shallower ring costs bandwidth, K blocks cost a carry array and restaging).
+  // Prefer the whole of x beside the ring; give up ring depth before cutting K into blocks (a
+  // shallower ring costs little, K blocks cost a carry array and restaging).
   for (;; --stages) {
     const size_t fixed = 1024 /* base alignment slack */ + 2 * kMaxStages * sizeof(uint64_t) +
-                         (size_t)stages * kStageBytes + 2 * kConsumerWarps * kOut * sizeof(float);
-    // Two CTAs per SM when everything fits twice (a dependent launch can then move in early).
-    const int per_sm = (2 * (fixed + XLayout<NC>::bytes(kpad) + 1024) <= 228 * 1024) ? 2 : 1;
+                         (size_t)stages * kStageBytes + (size_t)(stages + 1) * CW * kOut * sizeof(float) +
+                         (kMaxStages + 1) * sizeof(int);
+    need = fixed + XLayout<NC>::bytes(kpad);
+    kblk = kpad;
+    int per_sm = (int)(kSmPool / (need + 1024));
+    if (per_sm > max_per_sm) per_sm = max_per_sm;
+    if (per_sm < 1) per_sm = 1;
     grid = sms * per_sm;
     if (grid > p.ntiles) grid = p.ntiles;
     p.tiles_per_cta = (p.ntiles + grid - 1) / grid;
-    need = fixed + XLayout<NC>::bytes(kpad);
-    kblk = kpad;
     if (need <= kMaxSmem) break;
-    if (stages > 2) continue;
+    if (stages > 1) continue;
     // ... otherwise cut K into blocks of as many stages' worth as fit, leaving room for the carries.
+    grid = sms < p.ntiles ? sms : p.ntiles;
+    p.tiles_per_cta = (p.ntiles + grid - 1) / grid;
     const size_t carries = (size_t)p.tiles_per_cta * kOut * sizeof(float);
     if (fixed + carries + XLayout<NC>::bytes(KC) > kMaxSmem) return B200_ENOTREADY;   // caller falls back
     kblk = (int)((kMaxSmem - fixed - carries) / XLayout<NC>::bytes(KC)) * KC;
@@ -371,11 +427,11 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   p.nstages = stages;
   p.kblk = kblk;
 
-  auto kern = q4f16_gemv_pipe_kernel<NC>;
+  auto kern = q4f16_gemv_pipe_kernel<NC, CW, CH, DBG>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
   if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemv: cudaFuncSetAttribute(%zu): %s", need, cudaGetErrorString(e));
   // Ask for the largest shared-memory carve-out: the default picks the smallest that fits ONE CTA,
-  // which would keep a second CTA (or the next dependent launch) off the SM.
+  // which would keep further CTAs (or the next dependent launch) off the SM.
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
@@ -393,6 +449,16 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   return B200_OK;
 }
 
+template <int CW, int CH>
+int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int m, int n, int k,
+                  cudaStream_t stream) {
+  if (m == 1) return launch_pipe<1, CW, CH>(x, wq, scales, y, m, n, k, stream);
+  if (m == 2) return launch_pipe<2, CW, CH>(x, wq, scales, y, m, n, k, stream);
+  if (m <= 4) return launch_pipe<4, CW, CH>(x, wq, scales, y, m, n, k, stream);
+  if (m <= 8) return launch_pipe<8, CW, CH>(x, wq, scales, y, m, n, k, stream);
+  return launch_pipe<16, CW, CH>(x, wq, scales, y, m, n, k, stream);
+}
+
 }  // namespace
 
 // Returns B200_ENOTREADY when the shape is outside what this kernel takes (caller falls back to
@@ -401,11 +467,18 @@ int launch_gemv_pipe(const __half* x, const uint32_t* wq, const __half* scales, 
                      int64_t K, cudaStream_t stream) {
   if (K % 256 != 0 || (reinterpret_cast<uintptr_t>(scales) & 15u)) return B200_ENOTREADY;
   int m = (int)M, n = (int)N, k = (int)K;
-  if (m == 1) return launch_pipe<1>(x, wq, scales, y, m, n, k, stream);
-  if (m == 2) return launch_pipe<2>(x, wq, scales, y, m, n, k, stream);
-  if (m <= 4) return launch_pipe<4>(x, wq, scales, y, m, n, k, stream);
-  if (m <= 8) return launch_pipe<8>(x, wq, scales, y, m, n, k, stream);
-  return launch_pipe<16>(x, wq, scales, y, m, n, k, stream);
+  const int warps = (int)options().gemv_warps;     // 0 = auto
+  const int chunks = (int)options().gemv_chunks;   // 0 = auto
+  if (warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_debug == 1 && m == 1) return launch_pipe<1, 8, 16, 1>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_debug == 2 && m == 1) return launch_pipe<1, 8, 16, 2>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_debug == 3 && m == 1) return launch_pipe<1, 8, 16, 3>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_debug == 4 && m == 1) return launch_pipe<1, 8, 16, 4>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_debug == 6 && m == 1) return launch_pipe<1, 8, 16, 6>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_debug == 7 && m == 1) return launch_pipe<1, 8, 16, 7>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_debug == 5 && m == 1) return launch_pipe<1, 16, 16, 4>(x, wq, scales, y, m, n, k, stream);
+  if (chunks == 16) return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream);
+  return launch_pipe_m<8, 8>(x, wq, scales, y, m, n, k, stream);
 }
 
 int gemv_pipe_error_read_and_clear() {
