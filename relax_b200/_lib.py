@@ -9,7 +9,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200_q4f16.so")
+LIB_PATH = os.environ.get("B200_Q4F16_LIB") or os.path.join(_HERE, "libb200_q4f16.so")
 
 OK, EINVAL, ENODEVICE, ELAUNCH, EDEVICE, ENOTREADY = 0, -1, -2, -3, -4, -5
 

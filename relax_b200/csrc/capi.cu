@@ -190,8 +190,6 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "gemv.warps")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.warps in 0..16"); o.gemv_warps = v; }
   else if (!strcmp(name, "gemv.stages")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.stages in 0..16"); o.gemv_stages = v; }
   else if (!strcmp(name, "gemv.pdl")) { o.gemv_pdl = v != 0; }
-  else if (!strcmp(name, "gemv.debug")) { o.gemv_debug = v; }
-  else if (!strcmp(name, "gemv.chunks")) { if (v != 0 && v != 8 && v != 16) return fail(B200_EINVAL, "gemv.chunks is 0, 8 or 16"); o.gemv_chunks = v; }
   else if (!strcmp(name, "gemv.ctas_per_sm")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemv.ctas_per_sm in 0..8"); o.gemv_ctas_per_sm = v; }
   else if (!strcmp(name, "gemm.variant")) { if (v < 0 || v > 63) return fail(B200_EINVAL, "gemm.variant in 0..63"); o.gemm_variant = v; }
   else if (!strcmp(name, "gemm.stages")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemm.stages in 0..8"); o.gemm_stages = v; }
@@ -207,7 +205,6 @@ int64_t b200_get_option(const char* name) {
   if (!strcmp(name, "gemv.warps")) return o.gemv_warps;
   if (!strcmp(name, "gemv.stages")) return o.gemv_stages;
   if (!strcmp(name, "gemv.pdl")) return o.gemv_pdl;
-  if (!strcmp(name, "gemv.chunks")) return o.gemv_chunks;
   if (!strcmp(name, "gemv.ctas_per_sm")) return o.gemv_ctas_per_sm;
   if (!strcmp(name, "gemm.variant")) return o.gemm_variant;
   if (!strcmp(name, "gemm.stages")) return o.gemm_stages;

@@ -91,13 +91,13 @@ struct PipeParams {
 
 // Shared memory carve-up (after rounding the base up to 1024 bytes):
 //   ring: nstages * kStageBytes
-//   [.., +8*2*kMaxStages)          full / empty mbarriers
+//   bars: full[kMaxStages] empty[kMaxStages] red_full[kMaxStages+1] red_empty[kMaxStages+1]
 //   xs:   XLayout::bytes(kblk)     permuted x block
-//   red:  (nstages+1) * CW * MT*128 * 4   cross-warp partial sums; a warp is never more than
-//                                  nstages tiles ahead of the slowest one (stage hand-back needs all)
-//   cnt:  (nstages+1) ints         warps arrived per buffer
+//   red:  (nstages+1) * CW * MT*128 * 4   per-warp partial sums of a tile, one buffer per tile in flight
 //   accs: tiles_per_cta * MT*128*4 (only when K is cut into several blocks)
-template <int NC, int CW, int CH, int DBG = 0>
+//
+// Warps: CW consumers, then one TMA warp (two issuing lanes), then one epilogue warp.
+template <int NC, int CW, int CH>
 __global__ void __launch_bounds__((CW + 2) * 32, 1)
 q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   constexpr int MT = (NC + 7) / 8;
@@ -115,11 +115,12 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   unsigned char* ring = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)p.nstages * kStageBytes);
   uint64_t* empty = full + kMaxStages;
-  uint4* xs = reinterpret_cast<uint4*>(empty + kMaxStages);
+  uint64_t* red_full = empty + kMaxStages;
+  uint64_t* red_empty = red_full + kMaxStages + 1;
+  uint4* xs = reinterpret_cast<uint4*>(red_empty + kMaxStages + 1);
   float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + XLayout<NC>::bytes(p.kblk));
   const int nred = p.nstages + 1;
-  int* cnt = reinterpret_cast<int*>(red + nred * CW * kOut);
-  float* accs = reinterpret_cast<float*>(cnt + kMaxStages + 1);
+  float* accs = red + nred * CW * kOut;
 
   __shared__ int s_abort;                    // set once a bounded wait gives up: later waits are skipped
 
@@ -130,21 +131,25 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
 
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s <= kMaxStages; ++s) cnt[s] = 0;
     for (int s = 0; s < p.nstages; ++s) {
       mbar_init(&full[s], 2);
       mbar_init(&empty[s], CW);
+    }
+    for (int s = 0; s < nred; ++s) {
+      mbar_init(&red_full[s], CW);
+      mbar_init(&red_empty[s], 1);
     }
     mbar_fence_init();
   }
   __syncthreads();
   pdl_launch_dependents();
 
-  if (warp >= CW) {
-    // ------------------------------------------------------------------ producer warps
-    // warp CW loads the packed weights, warp CW+1 the scales: one tiled load per stage each.
-    const bool is_w = warp == CW;
-    if (lane == 0) {
+  if (warp == CW) {
+    // ------------------------------------------------------------------ producer warp
+    // lane 0 loads the packed weights, lane 1 the scales: one tiled load per stage each (the two
+    // lanes run as independent threads; one thread issuing both would halve the issue rate).
+    const bool is_w = lane == 0;
+    if (lane < 2) {
       prefetch_tmap(is_w ? &p.tm_w : &p.tm_s);
       const uint64_t policy = policy_evict_first();
       int s = 0;
@@ -155,7 +160,6 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
           const int row0 = tile * kRows;
           for (int k0 = k_lo; k0 < k_hi; k0 += KC, s = (s + 1 == p.nstages ? 0 : s + 1), round += (s == 0)) {
-            if (DBG >= 4 && round > 0) continue;
             if (round > 0) {
               // Legitimately as long as the previous kernel in the stream runs (the consumers
               // that free the stages sit in griddepcontrol.wait until then): bound it by time.
@@ -181,6 +185,50 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     return;
   }
 
+  if (warp == CW + 1) {
+    // ------------------------------------------------------------------ epilogue warp
+    // Adds up the CW partial sums of each finished tile in warp order (the result does not depend
+    // on which consumer finished last), carries them across K blocks, stores fp16.
+    pdl_wait();                                  // y may still be read by the previous kernel
+    int rb = 0;
+    uint32_t rround = 0;
+    for (int kb = 0; kb < nkb; ++kb) {
+      int slot = 0;
+      for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++slot) {
+        if (!mbar_try_wait(&red_full[rb], rround & 1)) {
+          if (!*(volatile int*)&s_abort && !mbar_wait_ns_relaxed(&red_full[rb], rround & 1, kProducerWaitNs)) {
+            atomicExch(&g_gemv_pipe_error, 4);
+            *(volatile int*)&s_abort = 1;
+          }
+        }
+        const float* rbuf = red + rb * (CW * kOut);
+#pragma unroll
+        for (int q = 0; q < 4 * MT; ++q) {
+          const int e = q * 32 + lane;
+          float sum = 0.f;
+#pragma unroll
+          for (int w2 = 0; w2 < CW; ++w2) sum += rbuf[w2 * kOut + e];
+          if (nkb > 1) {
+            float* a = accs + slot * kOut + e;
+            if (kb > 0) sum += *a;
+            if (kb < nkb - 1) *a = sum;
+          }
+          if (kb == nkb - 1) {
+            const int i = q & 3, mt = q >> 2;
+            const int row = tile * kRows + (lane >> 2) + 8 * (i >> 1);
+            const int col = mt * 8 + 2 * (lane & 3) + (i & 1);
+            if (row < p.N && col < p.M) p.y[(int64_t)col * p.N + row] = __float2half_rn(sum);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&red_empty[rb]);
+        rb = rb + 1 == nred ? 0 : rb + 1;
+        rround += (rb == 0);
+      }
+    }
+    return;
+  }
+
   // -------------------------------------------------------------------- consumer warps
   const int g = lane >> 2;
   const int t = lane & 3;
@@ -191,7 +239,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   //   (same swizzle phase).  Words 2t and 2t+1 differ in bit 4 only.
   const uint32_t w_off = (uint32_t)((warp * kRows + g) * 128 + (((2 * t) ^ g) << 4));
   const uint32_t s_off = (uint32_t)(kWBytes + (warp * kRows + g) * 16 + t * 4);
-  // x: words 32*chunk + 8t + i of the staged block, column g (the k-block offset is added per stage)
+  // x: words 32*chunk + 8t + i of the staged block, column g (the k-block offset is added per stage).
   // Lanes whose batch column does not exist (g >= NC) read column 0: what they feed into the MMA
   // only reaches output columns >= NC, which are never stored.
   const uint4* x_thr = xs + (NC >= 8 ? (warp * 32 + 8 * t) * NC + (g ^ (2 * t)) : NC * (warp * 36 + 9 * t) + (g < NC ? g : 0));
@@ -201,9 +249,41 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   const Q4Consts qc = q4_consts();
   pdl_wait();                                    // x may be the previous kernel's output
 
+  // Two accumulation chains over the whole tile: consecutive MMAs alternate between them so the
+  // tensor pipe never waits on its own result.
+  float acc[2][MT][4];
+
+  // One chunk (rows g and g+8, groups 2t and 2t+1) into the accumulators.  The weights are
+  // rounded to fp16 exactly as the reference does: (q-7) * scale, one HMUL2 per pair.
+  auto chunk = [&](const uint4 (&w)[2][2], const uint32_t (&sc)[2], const uint4* xu) {
+    const __half2 sp0 = u32_as_h2(sc[0]), sp1 = u32_as_h2(sc[1]);   // (scale of group 2t, of group 2t+1)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __half2 s0 = h ? __high2half2(sp0) : __low2half2(sp0);
+      const __half2 s1 = h ? __high2half2(sp1) : __low2half2(sp1);
+      const uint32_t wr0[4] = {w[0][h].x, w[0][h].y, w[0][h].z, w[0][h].w};
+      const uint32_t wr1[4] = {w[1][h].x, w[1][h].y, w[1][h].z, w[1][h].w};
+#pragma unroll
+      for (int wd = 0; wd < 4; ++wd) {
+        uint4 b[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) b[mt] = xu[(4 * h + wd) * NC + 8 * mt];
+        uint32_t a_lo[4], a_hi[4];
+        q4_dequant_pairs(wr0[wd], s0, a_lo, qc);
+        q4_dequant_pairs(wr1[wd], s1, a_hi, qc);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_16x8x16(acc[0][mt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[mt].x, b[mt].y);
+          mma_16x8x16(acc[1][mt], a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[mt].z, b[mt].w);
+        }
+      }
+    }
+  };
+
   int s = 0;                                     // ring slot of the current stage
   uint32_t round = 0;                            // how many times the ring has wrapped
   int rb = 0;                                    // reduction buffer of the current tile
+  uint32_t rround = 0;
   for (int kb = 0; kb < nkb; ++kb) {
     const int k_lo = kb * p.kblk;
     const int k_hi = min(p.K, k_lo + p.kblk);
@@ -226,21 +306,17 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     }
     bar_sync(1, kConsumers);
 
-    int slot = 0;
-    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++slot) {
-      float acc[2][MT][4];
+    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
 #pragma unroll
-      for (int a = 0; a < 2; ++a)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
+        for (int i = 0; i < 4; ++i) acc[0][mt][i] = acc[1][mt][i] = 0.f;
 
       const uint4* xk = x_thr;
       for (int k0 = k_lo; k0 < k_hi; k0 += KC, xk += kXStage, s = (s + 1 == p.nstages ? 0 : s + 1), round += (s == 0)) {
         // On a timeout the kernel keeps going without waiting (results are garbage, the error
         // flag says so) so that every warp still reaches the named barriers and the CTA ends.
-        if ((DBG < 4 || round == 0) && !mbar_try_wait(&full[s], round & 1)) {
+        if (!mbar_try_wait(&full[s], round & 1)) {
           if (!*(volatile int*)&s_abort && !mbar_wait_ns(&full[s], round & 1, kConsumerWaitNs)) {
             atomicExch(&g_gemv_pipe_error, 2);
             *(volatile int*)&s_abort = 1;
@@ -270,88 +346,38 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
           pin_loaded(sc[u][0]);
           pin_loaded(sc[u][1]);
         }
-        if (DBG != 6 && DBG != 7) fence_proxy_async_smem();   // generic reads ordered before the TMA refill (async proxy)
-        if (DBG != 7) __syncwarp();
-        if (DBG != 7 && lane == 0) mbar_arrive(&empty[s]);            // all of this warp's share is in registers
+        fence_proxy_async_smem();   // generic reads ordered before the TMA refill (async proxy)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);            // all of this warp's share is in registers
 
+        if (k0 + KC <= k_hi) {
+          // whole stage inside K: straight-line code over this warp's chunks
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
+          for (int u = 0; u < U; ++u) chunk(w[u], sc[u], xk + u * kXUnit);
+        } else {
           // chunks past K were zero-filled: nothing to add
-          if (k0 + (warp + u * CW) * 256 >= k_hi) continue;
-          const uint4* xu = xk + u * kXUnit;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const __half2 sp0 = u32_as_h2(sc[u][0]), sp1 = u32_as_h2(sc[u][1]);
-            const __half2 s0 = h ? __high2half2(sp0) : __low2half2(sp0);
-            const __half2 s1 = h ? __high2half2(sp1) : __low2half2(sp1);
-            const uint32_t wr0[4] = {w[u][0][h].x, w[u][0][h].y, w[u][0][h].z, w[u][0][h].w};
-            const uint32_t wr1[4] = {w[u][1][h].x, w[u][1][h].y, w[u][1][h].z, w[u][1][h].w};
-#pragma unroll
-            for (int wd = 0; wd < 4; ++wd) {
-              uint4 b[MT];
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) b[mt] = xu[(4 * h + wd) * NC + 8 * mt];
-              uint32_t a_lo[4], a_hi[4];
-              if (DBG == 1) {
-                acc[0][0][0] += __uint_as_float((wr0[wd] ^ wr1[wd] ^ b[0].x ^ h2_as_u32(s0) ^ h2_as_u32(s1)) & 0x007fffffu);
-                continue;
-              }
-              if (DBG == 2) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) { a_lo[i] = wr0[wd] + i + h2_as_u32(s0); a_hi[i] = wr1[wd] - i + h2_as_u32(s1); }
-              } else {
-                q4_dequant_pairs(wr0[wd], s0, a_lo, qc);
-                q4_dequant_pairs(wr1[wd], s1, a_hi, qc);
-              }
-              if (DBG == 3) {
-                acc[0][0][0] += __uint_as_float((a_lo[0] ^ a_lo[1] ^ a_lo[2] ^ a_lo[3] ^ a_hi[0] ^ a_hi[1] ^ a_hi[2] ^ a_hi[3] ^ b[0].x) & 0x007fffffu);
-                continue;
-              }
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) {
-                mma_16x8x16(acc[0][mt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[mt].x, b[mt].y);
-                mma_16x8x16(acc[1][mt], a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[mt].z, b[mt].w);
-              }
-            }
-          }
+          for (int u = 0; u < U; ++u)
+            if (k0 + (warp + u * CW) * 256 < k_hi) chunk(w[u], sc[u], xk + u * kXUnit);
         }
       }
 
-      // ---- cross-warp reduction of this (tile, k block): the last warp to arrive does it ---------------
-      float* rbuf = red + rb * (CW * kOut);
+      // ---- hand this warp's partial sums of the tile to the epilogue warp --------------------------
+      if (rround > 0 && !mbar_try_wait(&red_empty[rb], (rround - 1) & 1)) {
+        if (!*(volatile int*)&s_abort && !mbar_wait_ns(&red_empty[rb], (rround - 1) & 1, kConsumerWaitNs)) {
+          atomicExch(&g_gemv_pipe_error, 8);
+          *(volatile int*)&s_abort = 1;
+        }
+      }
+      float* rbuf = red + rb * (CW * kOut) + warp * kOut + lane;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) rbuf[warp * kOut + (mt * 4 + i) * 32 + lane] = acc[0][mt][i] + acc[1][mt][i];
-      __threadfence_block();
+        for (int i = 0; i < 4; ++i) rbuf[(mt * 4 + i) * 32] = acc[0][mt][i] + acc[1][mt][i];
       __syncwarp();
-      int arrived = 0;
-      if (lane == 0) arrived = atomicAdd(&cnt[rb], 1);
-      arrived = __shfl_sync(0xffffffffu, arrived, 0);
-      if (arrived == CW - 1) {
-        __threadfence_block();
-#pragma unroll
-        for (int q = 0; q < 4 * MT; ++q) {
-          const int e = q * 32 + lane;
-          float sum = 0.f;
-#pragma unroll
-          for (int w2 = 0; w2 < CW; ++w2) sum += rbuf[w2 * kOut + e];
-          if (nkb > 1) {
-            float* a = accs + slot * kOut + e;
-            if (kb > 0) sum += *a;
-            if (kb < nkb - 1) *a = sum;
-          }
-          if (kb == nkb - 1) {
-            const int i = q & 3, mt = q >> 2;
-            const int row = tile * kRows + (lane >> 2) + 8 * (i >> 1);
-            const int col = mt * 8 + 2 * (lane & 3) + (i & 1);
-            if (row < p.N && col < p.M) p.y[(int64_t)col * p.N + row] = __float2half_rn(sum);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) cnt[rb] = 0;              // the buffer comes round again nstages+1 tiles later
-      }
+      if (lane == 0) mbar_arrive(&red_full[rb]);   // release: the stores above are visible to the waiter
       rb = rb + 1 == nred ? 0 : rb + 1;
+      rround += (rb == 0);
     }
   }
   if (*(volatile int*)&s_abort) {
@@ -361,7 +387,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   }
 }
 
-template <int NC, int CW, int CH, int DBG = 0>
+template <int NC, int CW, int CH>
 int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int M, int N, int K,
                 cudaStream_t stream) {
   constexpr int MT = (NC + 7) / 8;
@@ -388,32 +414,48 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   const int kpad = ((K + KC - 1) / KC) * KC;
   const int stages_per_tile = kpad / KC;
   int stages = (int)options().gemv_stages;
-  if (stages <= 0) stages = stages_per_tile >= 2 ? 2 : 1;   // registers are the extra buffer: a shallow ring is enough
+  // Registers are the second buffer (a stage is handed back as soon as it has been copied out) and
+  // two CTAs share an SM, so one stage per CTA measured fastest; deeper rings only cost shared memory.
+  if (stages <= 0) stages = 1;
+  (void)stages_per_tile;
   if (stages > kMaxStages) stages = kMaxStages;
   const size_t kMaxSmem = 227 * 1024;
-  const size_t kSmPool = 228 * 1024;   // shared memory per SM, 1 KB of it reserved per resident CTA
   const int sms = sm_count();
+  auto kern = q4f16_gemv_pipe_kernel<NC, CW, CH>;
+  // Ask for the largest shared-memory carve-out: the default picks the smallest that fits ONE CTA,
+  // which would keep further CTAs (or the next dependent launch) off the SM.
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   int max_per_sm = (int)options().gemv_ctas_per_sm;
-  if (max_per_sm <= 0) max_per_sm = 4;
-  const int by_threads = 2048 / kThreads;
-  if (max_per_sm > by_threads) max_per_sm = by_threads;
+  if (max_per_sm <= 0) max_per_sm = 2;
   size_t need = 0;
   int kblk = 0, grid = 0;
   // Prefer the whole of x beside the ring; give up ring depth before cutting K into blocks (a
   // shallower ring costs little, K blocks cost a carry array and restaging).
   for (;; --stages) {
-    const size_t fixed = 1024 /* base alignment slack */ + 2 * kMaxStages * sizeof(uint64_t) +
-                         (size_t)stages * kStageBytes + (size_t)(stages + 1) * CW * kOut * sizeof(float) +
-                         (kMaxStages + 1) * sizeof(int);
+    const size_t fixed = 1024 /* base alignment slack */ + (4 * kMaxStages + 2) * sizeof(uint64_t) +
+                         (size_t)stages * kStageBytes + (size_t)(stages + 1) * CW * kOut * sizeof(float);
     need = fixed + XLayout<NC>::bytes(kpad);
     kblk = kpad;
-    int per_sm = (int)(kSmPool / (need + 1024));
-    if (per_sm > max_per_sm) per_sm = max_per_sm;
-    if (per_sm < 1) per_sm = 1;
-    grid = sms * per_sm;
-    if (grid > p.ntiles) grid = p.ntiles;
-    p.tiles_per_cta = (p.ntiles + grid - 1) / grid;
-    if (need <= kMaxSmem) break;
+    if (need <= kMaxSmem) {
+      // resident CTAs per SM as the hardware will place them (registers and threads count too);
+      // the answer for the last shared-memory size is remembered (per thread, per kernel variant)
+      static thread_local size_t cached_need = 0;
+      static thread_local int cached_per_sm = 0;
+      if (cached_need != need) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+        if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemv: cudaFuncSetAttribute(%zu): %s", need, cudaGetErrorString(e));
+        int q = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, kThreads, need) != cudaSuccess || q < 1) q = 1;
+        cached_need = need;
+        cached_per_sm = q;
+      }
+      int per_sm = cached_per_sm;
+      if (per_sm > max_per_sm) per_sm = max_per_sm;
+      grid = sms * per_sm;
+      if (grid > p.ntiles) grid = p.ntiles;
+      p.tiles_per_cta = (p.ntiles + grid - 1) / grid;
+      break;
+    }
     if (stages > 1) continue;
     // ... otherwise cut K into blocks of as many stages' worth as fit, leaving room for the carries.
     grid = sms < p.ntiles ? sms : p.ntiles;
@@ -422,17 +464,14 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
     if (fixed + carries + XLayout<NC>::bytes(KC) > kMaxSmem) return B200_ENOTREADY;   // caller falls back
     kblk = (int)((kMaxSmem - fixed - carries) / XLayout<NC>::bytes(KC)) * KC;
     need = fixed + carries + XLayout<NC>::bytes(kblk);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+    if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemv: cudaFuncSetAttribute(%zu): %s", need, cudaGetErrorString(e));
     break;
   }
   p.nstages = stages;
   p.kblk = kblk;
 
-  auto kern = q4f16_gemv_pipe_kernel<NC, CW, CH, DBG>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
-  if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemv: cudaFuncSetAttribute(%zu): %s", need, cudaGetErrorString(e));
-  // Ask for the largest shared-memory carve-out: the default picks the smallest that fits ONE CTA,
-  // which would keep further CTAs (or the next dependent launch) off the SM.
-  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaError_t e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(kThreads);
@@ -467,18 +506,8 @@ int launch_gemv_pipe(const __half* x, const uint32_t* wq, const __half* scales, 
                      int64_t K, cudaStream_t stream) {
   if (K % 256 != 0 || (reinterpret_cast<uintptr_t>(scales) & 15u)) return B200_ENOTREADY;
   int m = (int)M, n = (int)N, k = (int)K;
-  const int warps = (int)options().gemv_warps;     // 0 = auto
-  const int chunks = (int)options().gemv_chunks;   // 0 = auto
-  if (warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream);
-  if (options().gemv_debug == 1 && m == 1) return launch_pipe<1, 8, 16, 1>(x, wq, scales, y, m, n, k, stream);
-  if (options().gemv_debug == 2 && m == 1) return launch_pipe<1, 8, 16, 2>(x, wq, scales, y, m, n, k, stream);
-  if (options().gemv_debug == 3 && m == 1) return launch_pipe<1, 8, 16, 3>(x, wq, scales, y, m, n, k, stream);
-  if (options().gemv_debug == 4 && m == 1) return launch_pipe<1, 8, 16, 4>(x, wq, scales, y, m, n, k, stream);
-  if (options().gemv_debug == 6 && m == 1) return launch_pipe<1, 8, 16, 6>(x, wq, scales, y, m, n, k, stream);
-  if (options().gemv_debug == 7 && m == 1) return launch_pipe<1, 8, 16, 7>(x, wq, scales, y, m, n, k, stream);
-  if (options().gemv_debug == 5 && m == 1) return launch_pipe<1, 16, 16, 4>(x, wq, scales, y, m, n, k, stream);
-  if (chunks == 16) return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream);
-  return launch_pipe_m<8, 8>(x, wq, scales, y, m, n, k, stream);
+  if (options().gemv_warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream);
+  return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream);
 }
 
 int gemv_pipe_error_read_and_clear() {

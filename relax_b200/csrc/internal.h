@@ -18,8 +18,6 @@ struct Options {
   int64_t gemv_warps = 0;     // 0 = auto
   int64_t gemv_stages = 0;    // 0 = auto (bulk-copy pipeline depth)
   int64_t gemv_pdl = 1;       // programmatic dependent launch on the streaming kernels
-  int64_t gemv_debug = 0;
-  int64_t gemv_chunks = 0;    // 0 = auto: 256-k chunks per pipeline stage (8 or 16)
   int64_t gemv_ctas_per_sm = 0;  // 0 = auto: cap on resident CTAs per SM used to size the grid
   int64_t gemm_variant = 0;   // 0 = auto
   int64_t gemm_stages = 0;
