@@ -5,9 +5,13 @@
 // route would be a MetaSchedule-tuned mma.sync kernel, src/relax/transform/meta_schedule.cc).
 // Tensor-core bound: 2*M*N*K flop against N*K/2 bytes of weights.
 //
-// One persistent CTA per SM, output tile 128 tokens x 256 weight rows, K in blocks of 64:
+// One persistent CTA per SM, output tile 256 tokens x 256 weight rows, K in blocks of 64.  The
+// tile is two 128-token halves that share every dequantised weight block: the int4 -> fp16
+// conversion runs on the CUDA cores at roughly the rate one 128x256 MMA stream consumes it, so
+// each converted block has to feed two of them for the tensor pipe to be the limit.
 //
-//   warp 0      TMA producer for x: box {64 k, 128 rows} fp16, 128-byte swizzle -> ring A
+//   warp 0      TMA producer for x: box {64 k, 256 rows} fp16, 128-byte swizzle -> ring A
+//               (rows 0-127 and 128-255 of the box are the two halves' A operands)
 //   warp 2      TMA producer for the packed weights (box {16 words = 128 k, 256 rows}, 64-byte
 //               swizzle) and, when the scale rows are 16-byte aligned, for the scales (box
 //               {8 groups = 256 k, 256 rows}) -> rings RAW / SC
@@ -17,12 +21,12 @@
 //               c at position c ^ (r % 8): the canonical K-major SWIZZLE_128B layout a TMA load
 //               would have produced -> ring B (generic-proxy stores, fence.proxy.async, mbarrier)
 //   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16 (M=128, N=256,
-//               K=16) four times per K block, A and B from shared-memory descriptors, fp32
-//               accumulator in TMEM; tcgen05.commit hands the A and B stages back and, after the
-//               last K block, publishes the accumulator.  TMEM holds two 256-column accumulators
-//               so the epilogue of tile i overlaps the main loop of tile i+1.
+//               K=16) four times per K block and half, A and B from shared-memory descriptors,
+//               fp32 accumulators in TMEM (all 512 columns: 256 per half); tcgen05.commit hands
+//               the A and B stages back and, after the last K block, publishes each half.
 //   warps 4-7   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, fp32 -> fp16 (RN), 16-byte
-//               global stores into row-major y.
+//               global stores into row-major y.  The halves are drained in order and handed back
+//               one by one, so the next tile's MMAs on half 0 start while half 1 is still drained.
 //
 // Out-of-range rows (M, N tails) and columns (K tail) are zero-filled by the TMA unit: a zero
 // scale makes the weight +-0, a zero x makes the product 0, the epilogue skips them.
@@ -41,14 +45,15 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BM = 128;            // tokens per tile (UMMA M)
+constexpr int BM = 128;            // tokens per half tile (UMMA M)
+constexpr int BMT = 2 * BM;        // tokens per tile: two halves share each dequantised weight block
 constexpr int BN = 256;            // weight rows per tile (UMMA N)
 constexpr int BK = 64;             // k per MMA stage (one 128-byte swizzled row of fp16)
-constexpr int SA = 4;              // x stages
-constexpr int SB = 3;              // dequantised-weight stages
+constexpr int SA = 3;              // x stages
+constexpr int SB = 2;              // dequantised-weight stages
 constexpr int SR = 2;              // packed-weight stages (128 k each = two K blocks)
 constexpr int SS = 2;              // scale stages (256 k each = four K blocks)
-constexpr int kABytes = BM * BK * 2;          // 16384
+constexpr int kABytes = BMT * BK * 2;         // 32768: half h at +h*16384
 constexpr int kBBytes = BN * BK * 2;          // 32768
 constexpr int kRawBytes = BN * 64;            // 16384: 256 rows x 16 words
 constexpr int kScBytes = BN * 16;             // 4096:  256 rows x 8 scales
@@ -67,13 +72,13 @@ struct Smem {
   uint64_t b_full[SB], b_empty[SB];
   uint64_t raw_full[SR], raw_empty[SR];
   uint64_t sc_full[SS], sc_empty[SS];
-  uint64_t acc_full[2], acc_empty[2];
+  uint64_t acc_full[2], acc_empty[2];   // one pair per half
   uint32_t tmem_base;
   int abort_flag;
 };
 
 struct GemmParams {
-  CUtensorMap tm_x;    // fp16   {K, M},     box {64, 128}, SWIZZLE_128B
+  CUtensorMap tm_x;    // fp16   {K, M},     box {64, 256}, SWIZZLE_128B
   CUtensorMap tm_w;    // uint32 {K/8, N},   box {16, 256}, SWIZZLE_64B
   CUtensorMap tm_s;    // fp16   {K/32, N},  box {8, 256}   (only when scales_tma)
   const __half* scales;
@@ -82,6 +87,44 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int scales_tma;
 };
+
+// Work units of one CTA, in order.  Whole waves of 256-token tiles first; if the last, partial
+// wave has at most half as many tiles as there are CTAs, its tiles are cut into their two
+// 128-token halves and spread over twice as many CTAs (a half on its own converts the weights
+// for 128 tokens only, so it runs at the conversion rate, but the wave is half as long).
+struct Work {
+  int tn;        // weight-row tile
+  int tok0;      // first token
+  int nhalf;     // 128-token halves to compute (1 or 2)
+};
+__device__ __forceinline__ bool get_work(const GemmParams& p, int i, Work& w) {
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = (int)gridDim.x, b = (int)blockIdx.x;
+  const int full_waves = tiles / grid;
+  const int rem = tiles - full_waves * grid;
+  int tile, half = -1;
+  if (i < full_waves) {
+    tile = b + i * grid;
+  } else if (i == full_waves && rem > 0) {
+    if (2 * rem <= grid) {
+      if (b >= 2 * rem) return false;
+      tile = full_waves * grid + (b >> 1);
+      half = b & 1;
+    } else {
+      if (b >= rem) return false;
+      tile = full_waves * grid + b;
+    }
+  } else {
+    return false;
+  }
+  const int tm = tile % p.tiles_m;
+  w.tn = tile / p.tiles_m;
+  w.tok0 = tm * BMT + (half > 0 ? BM : 0);
+  w.nhalf = (half < 0 && w.tok0 + BM < p.M) ? 2 : 1;
+  // a second half that holds no token is still a unit (its CTA idles through it): every role
+  // sees the same list
+  return true;
+}
 
 // Bounded wait that also honours (and raises) the block-wide abort flag.
 __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
@@ -102,7 +145,6 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int num_tiles = p.tiles_m * p.tiles_n;
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -127,14 +169,14 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     if (lane == 0) {
       prefetch_tmap(&p.tm_x);
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int tm = tile % p.tiles_m;
+      Work w;
+      for (int i = 0; get_work(p, i, w); ++i) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % SA;
           const uint32_t round = it / SA;
           if (round > 0) wait_or_abort(&sm.a_empty[s], (round - 1) & 1, abort_flag, 1);
           mbar_arrive_expect_tx(&sm.a_full[s], kABytes);
-          tma_load_2d(sm.a[s], &p.tm_x, kb * BK, tm * BM, &sm.a_full[s]);
+          tma_load_2d(sm.a[s], &p.tm_x, kb * BK, w.tok0, &sm.a_full[s]);
         }
       }
     }
@@ -144,8 +186,9 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       prefetch_tmap(&p.tm_w);
       if (p.scales_tma) prefetch_tmap(&p.tm_s);
       uint32_t it_raw = 0, it_sc = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int tn = tile / p.tiles_m;
+      Work w;
+      for (int i = 0; get_work(p, i, w); ++i) {
+        const int tn = w.tn;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (p.scales_tma && (kb & 3) == 0) {
             const int s = it_sc % SS;
@@ -170,72 +213,83 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16_f32(BM, BN);
-      uint32_t it_a = 0, it_b = 0, it_acc = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it_acc) {
-        const int acc = it_acc & 1;
-        const uint32_t acc_round = it_acc >> 1;
-        if (acc_round > 0) wait_or_abort(&sm.acc_empty[acc], (acc_round - 1) & 1, abort_flag, 4);
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+      uint32_t it_a = 0, it_b = 0, it_tile = 0;
+      Work w;
+      for (int i = 0; get_work(p, i, w); ++i, ++it_tile) {
+        const int nhalf = w.nhalf;                            // second half all padding or not ours: skip it
         for (int kb = 0; kb < num_kb; ++kb, ++it_a, ++it_b) {
           const int sa = it_a % SA, sb = it_b % SB;
           wait_or_abort(&sm.a_full[sa], (it_a / SA) & 1, abort_flag, 5);
           wait_or_abort(&sm.b_full[sb], (it_b / SB) & 1, abort_flag, 6);
           tc_fence_after_sync();
-          const uint64_t da = umma_desc_k128(smem_u32(sm.a[sa]));
           const uint64_t db = umma_desc_k128(smem_u32(sm.b[sb]));
+          for (int h = 0; h < nhalf; ++h) {
+            if (kb == 0 && it_tile > 0) {
+              // the epilogue has drained this half of the previous tile
+              wait_or_abort(&sm.acc_empty[h], (it_tile - 1) & 1, abort_flag, 4);
+              tc_fence_after_sync();
+            }
+            const uint32_t d_tmem = tmem_base + (uint32_t)h * BN;
+            const uint64_t da = umma_desc_k128(smem_u32(sm.a[sa] + h * (BM * BK * 2)));
 #pragma unroll
-          for (int k16 = 0; k16 < BK / 16; ++k16) {
-            // advancing 16 fp16 along K inside the swizzled 128-byte row = +32 bytes = +2 in the
-            // descriptor's 16-byte address units
-            umma_f16_ss(d_tmem, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, (kb | k16) != 0);
+            for (int k16 = 0; k16 < BK / 16; ++k16) {
+              // advancing 16 fp16 along K inside the swizzled 128-byte row = +32 bytes = +2 in the
+              // descriptor's 16-byte address units
+              umma_f16_ss(d_tmem, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, (kb | k16) != 0);
+            }
+            if (kb == num_kb - 1) umma_commit(&sm.acc_full[h]);
           }
           umma_commit(&sm.a_empty[sa]);
           umma_commit(&sm.b_empty[sb]);
         }
-        umma_commit(&sm.acc_full[acc]);
+        // a skipped half still takes part in the hand-shake so that the parities stay in step
+        if (nhalf == 1) umma_commit(&sm.acc_full[1]);
       }
     }
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------------ epilogue
     const int ew = warp - 4;                       // TMEM lane quadrant this warp may read
-    uint32_t it_acc = 0;
+    uint32_t it_tile = 0;
     const bool vec_ok = (p.N % 8) == 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it_acc) {
-      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-      const int acc = it_acc & 1;
-      wait_or_abort(&sm.acc_full[acc], (it_acc >> 1) & 1, abort_flag, 7);
-      tc_fence_after_sync();
-      const int row = tm * BM + ew * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)acc * BN;
+    Work w;
+    for (int i = 0; get_work(p, i, w); ++i, ++it_tile) {
+      const int tn = w.tn;
+      for (int h = 0; h < 2; ++h) {
+        wait_or_abort(&sm.acc_full[h], it_tile & 1, abort_flag, 7);
+        tc_fence_after_sync();
+        const int row = w.tok0 + h * BM + ew * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)h * BN;
+        if (h < w.nhalf && w.tok0 + h * BM < p.M) {  // (warp-uniform) half computed and holds real tokens
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
-          __half* dst = p.y + (int64_t)row * p.N + col0;
-          if (vec_ok && col0 + 32 <= p.N) {
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, v);
+            tmem_ld_wait();
+            const int col0 = tn * BN + c * 32;
+            if (row < p.M && col0 < p.N) {
+              __half* dst = p.y + (int64_t)row * p.N + col0;
+              if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1])));
-              o.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])));
-              o.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])));
-              o.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
-              *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+                for (int q = 0; q < 4; ++q) {
+                  uint4 o;
+                  o.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1])));
+                  o.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])));
+                  o.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])));
+                  o.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+                  *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+                }
+              } else {
+#pragma unroll
+                for (int q = 0; q < 32; ++q)
+                  if (col0 + q < p.N) dst[q] = __float2half_rn(__uint_as_float(v[q]));
+              }
             }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 32; ++q)
-              if (col0 + q < p.N) dst[q] = __float2half_rn(__uint_as_float(v[q]));
           }
         }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.acc_empty[h]);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.acc_empty[acc]);
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ dequantisers
@@ -243,8 +297,9 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     const int r8 = r & 7;
     const Q4Consts qc = q4_consts();
     uint32_t it_raw = 0, it_sc = 0, it_b = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int tn = tile / p.tiles_m;
+    Work w;
+    for (int i = 0; get_work(p, i, w); ++i) {
+      const int tn = w.tn;
       const int grow = tn * BN + r;                 // global weight row (may be >= N: zero-filled)
       uint4 sc4 = make_uint4(0, 0, 0, 0);           // 8 scales of the current 256-k span
       uint4 pk[4];                                  // 16 packed words of the current 128-k span
@@ -338,7 +393,7 @@ int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __hal
   {
     const uint64_t d[2] = {(uint64_t)K, (uint64_t)M};
     const uint64_t s[1] = {(uint64_t)K * 2};
-    const uint32_t b[2] = {BK, BM};
+    const uint32_t b[2] = {BK, BMT};
     if ((rc = make_tmap(&p.tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   }
   {
@@ -359,12 +414,14 @@ int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __hal
   p.scales = scales;
   p.y = y;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_m = (int)((M + BMT - 1) / BMT);
   p.tiles_n = (int)((N + BN - 1) / BN);
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = sm_count();
   if (options().gemm_max_ctas > 0 && grid > options().gemm_max_ctas) grid = (int)options().gemm_max_ctas;
-  if (grid > tiles) grid = tiles;
+  // fewer tiles than CTAs: the tiles run as 128-token halves on twice as many CTAs (see get_work)
+  if (grid > 2 * tiles) grid = 2 * tiles;
+  else if (grid > tiles && grid < 2 * tiles) grid = tiles;
   const size_t smem = sizeof(Smem) + 1024;
   auto kern = q4f16_gemm_tcgen05_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
