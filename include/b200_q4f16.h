@@ -161,6 +161,14 @@ B200_API int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t m
 B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
                               void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);
 
+/* out[b,:] = table[ids[b],:]: fp16 table [vocab,H], int32 ids [B] on the device (ids are clamped
+ * to the table).  H % 8 == 0.  (reference: relax.take, python/tvm/relax/transform/legalize_ops.py:168) */
+B200_API int b200_embed_rows(const void* table, const void* ids, void* out, int64_t B, int64_t H, int64_t vocab,
+                             void* cuda_stream);
+
+/* *pos += delta on the device (pos: one int32). */
+B200_API int b200_advance_pos(void* pos, int64_t delta, void* cuda_stream);
+
 /* out[b,i] = silu(gu[b,i]) * gu[b,I+i]; gu fp16 [B,2I], out fp16 [B,I]; I % 8 == 0. */
 B200_API int b200_silu_mul(const void* gu, void* out, int64_t B, int64_t I, void* cuda_stream);
 

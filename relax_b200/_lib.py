@@ -66,6 +66,8 @@ PROTOTYPES = {
     "b200_attn_decode_scratch_bytes": (_i64, [_i64, _i64, _i64]),
     "b200_attn_decode": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_silu_mul": (_ci, [_vp, _vp, _i64, _i64, _vp]),
+    "b200_embed_rows": (_ci, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_advance_pos": (_ci, [_vp, _i64, _vp]),
     "b200_launch_count": (_i64, []),
     "b200_reset_launch_count": (None, []),
     "b200_device_error_flags": (_ci, []),

@@ -231,6 +231,28 @@ silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ out, int I, 
   *reinterpret_cast<uint4*>(out + b * I + i) = o;
 }
 
+// out[b,:] = table[ids[b],:] (fp16 rows of H, H % 8 == 0).  grid (B), 128 threads.
+__global__ void __launch_bounds__(128)
+embed_rows_kernel(const __half* __restrict__ table, const int* __restrict__ ids, __half* __restrict__ out, int H,
+                  int vocab) {
+  ptx::pdl_wait();
+  const int b = blockIdx.x;
+  int id = ids[b];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);          // clamp: never read outside the table
+  const uint4* src = reinterpret_cast<const uint4*>(table + (int64_t)id * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)b * H);
+  ptx::pdl_launch_dependents();
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// *pos += delta (one thread): advances the decode position on the device so that a captured
+// graph can be replayed token after token.
+__global__ void advance_pos_kernel(int* pos, int delta) {
+  ptx::pdl_wait();
+  ptx::pdl_launch_dependents();
+  if (threadIdx.x == 0 && blockIdx.x == 0) *pos += delta;
+}
+
 template <typename K, typename... A>
 int launch(const char* what, K kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
   cudaLaunchConfig_t cfg = {};
@@ -301,6 +323,24 @@ int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, co
   if (rc) return rc;
   return launch("attn_decode_combine", attn_decode_combine_kernel, dim3((unsigned)nh, (unsigned)B), dim3(128), 0, s,
                 (const float*)scratch, (const int*)pos, (__half*)out, (int)nh, nsplit);
+}
+
+int b200_embed_rows(const void* table, const void* ids, void* out, int64_t B, int64_t H, int64_t vocab, void* stream) {
+  if (B < 0 || H <= 0 || H % 8 != 0 || vocab <= 0) return fail(B200_EINVAL, "embed_rows: need H %% 8 == 0, vocab > 0");
+  if (B == 0) return B200_OK;
+  if (!table || !ids || !out) return fail(B200_EINVAL, "embed_rows: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  return launch("embed_rows", embed_rows_kernel, dim3((unsigned)B), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                (const __half*)table, (const int*)ids, (__half*)out, (int)H, (int)vocab);
+}
+
+int b200_advance_pos(void* pos, int64_t delta, void* stream) {
+  if (!pos) return fail(B200_EINVAL, "advance_pos: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  return launch("advance_pos", advance_pos_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), (int*)pos,
+                (int)delta);
 }
 
 int b200_silu_mul(const void* gu, void* out, int64_t B, int64_t I, void* stream) {

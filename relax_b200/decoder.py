@@ -1,0 +1,217 @@
+"""Decode-step harness for a Llama-style q4f16 decoder: the callers either side of the quantised
+matmul (RMSNorm, RoPE + KV cache, attention, SwiGLU) wired to the C-ABI kernels, optionally
+tensor-parallel with one NCCL all-reduce after each row-parallel matmul.
+
+torch is used for device memory, streams, CUDA graphs, the NCCL process group and the fp16
+lm_head GEMM (a plain library GEMM); every other kernel of a step is this library's.
+
+Layout per rank (world size t, hidden H, heads nh, head dim 128, intermediate I):
+
+    qkv   q4  [3*H/t, H]      rows = q heads | k heads | v heads of this rank
+    o     q4  [H, H/t]        row-parallel   -> all-reduce
+    gu    q4  [2*I_r, H]      rows = gate | up rows of this rank's slice of I
+    down  q4  [H, I_r]        row-parallel   -> all-reduce
+    KV    fp16 [B, max_ctx, nh/t, 128] per layer, K and V
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import numpy as np
+import torch
+
+from . import _lib, tp
+
+
+@dataclasses.dataclass
+class DecoderConfig:
+    hidden: int = 4096
+    heads: int = 32
+    inter: int = 11008
+    layers: int = 32
+    vocab: int = 32000
+    eps: float = 1e-5
+    theta: float = 10000.0
+    head_dim: int = 128
+
+    def __post_init__(self):
+        if self.hidden != self.heads * self.head_dim or self.head_dim != 128:
+            raise ValueError("the attention kernels take head_dim 128 and hidden = heads * 128")
+
+
+def rope_tables(max_pos: int, head_dim: int, theta: float, device):
+    half = head_dim // 2
+    inv = theta ** (-np.arange(half, dtype=np.float64) * 2.0 / head_dim)
+    ang = np.arange(max_pos, dtype=np.float64)[:, None] * inv[None, :]
+    cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(device)
+    sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(device)
+    return cos.contiguous(), sin.contiguous()
+
+
+def synth_layer_numpy(cfg: DecoderConfig, seed: int):
+    """Full (unsharded) random layer on the host: nibbles uniform 0..15, scales U(0.005, 0.02),
+    norm weights ~ N(1, 0.02).  Small configurations only (tests)."""
+    from . import synth
+
+    rng = np.random.default_rng(seed)
+    H, I = cfg.hidden, cfg.inter
+    w = {}
+    for name, (n, k) in (("qkv", (3 * H, H)), ("o", (H, H)), ("gu", (2 * I, H)), ("down", (H, I))):
+        w[name] = synth.make_weights(n, k, rng)
+    w["norm1"] = (1.0 + 0.02 * rng.standard_normal(H)).astype(np.float16)
+    w["norm2"] = (1.0 + 0.02 * rng.standard_normal(H)).astype(np.float16)
+    return w
+
+
+def synth_layer_torch(cfg: DecoderConfig, seed: int, device):
+    """Same distributions generated on the device (model-sized tensors)."""
+    from . import synth
+
+    H, I = cfg.hidden, cfg.inter
+    w = {}
+    for j, (name, (n, k)) in enumerate((("qkv", (3 * H, H)), ("o", (H, H)), ("gu", (2 * I, H)), ("down", (H, I)))):
+        w[name] = synth.make_weights_torch(n, k, seed * 16 + j, device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 16 + 9)
+    w["norm1"] = (1.0 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.float16)
+    w["norm2"] = (1.0 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.float16)
+    return w
+
+
+def to_device(layer: dict, device):
+    out = {}
+    for k, v in layer.items():
+        if isinstance(v, tuple):
+            out[k] = tuple(torch.from_numpy(np.ascontiguousarray(a)).to(device) if isinstance(a, np.ndarray) else a.to(device)
+                           for a in v)
+        elif isinstance(v, np.ndarray):
+            out[k] = torch.from_numpy(v).to(device)
+        else:
+            out[k] = v
+    return out
+
+
+class DecodeEngine:
+    """Buffers and kernel sequence of one decode step for `batch` sequences.
+
+    `layers` is a list of per-rank layer shards (see tp.shard_layer) on `device`; `embed` the fp16
+    embedding table [vocab, H]; `lm_head` fp16 [vocab_local, H] (rows of this rank's vocabulary
+    slice) or None to stop at the final norm; `final_norm` fp16 [H].
+    """
+
+    def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
+                 device, rank: int = 0, world: int = 1, group=None):
+        self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
+        self.rank, self.world, self.group = rank, world, group
+        self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
+        self.L = _lib.lib()
+        H, B = cfg.hidden, batch
+        self.nh_local = cfg.heads // world
+        if cfg.heads % world:
+            raise ValueError("heads must divide by the tensor-parallel size")
+        f16 = dict(dtype=torch.float16, device=self.device)
+        hl = H // world
+        il_max = max(l["inter_local"] for l in layers) if layers else cfg.inter
+        self.x = torch.zeros((B, H), **f16)            # residual stream
+        self.h = torch.zeros((B, H), **f16)            # normalised activations
+        self.qkv = torch.zeros((B, 3 * hl), **f16)
+        self.q = torch.zeros((B, self.nh_local, 128), **f16)
+        self.attn = torch.zeros((B, hl), **f16)
+        self.o = torch.zeros((B, H), **f16)
+        self.gu = torch.zeros((B, 2 * il_max), **f16)
+        self.act = torch.zeros((B, il_max), **f16)
+        self.down = torch.zeros((B, H), **f16)
+        self.kc = [torch.zeros((B, max_ctx, self.nh_local, 128), **f16) for _ in layers]
+        self.vc = [torch.zeros((B, max_ctx, self.nh_local, 128), **f16) for _ in layers]
+        nbytes = int(self.L.b200_attn_decode_scratch_bytes(B, self.nh_local, max_ctx))
+        self.scratch = torch.empty((max(nbytes, 4) // 4,), dtype=torch.float32, device=self.device)
+        self.pos = torch.zeros((1,), dtype=torch.int32, device=self.device)
+        self.tokens = torch.zeros((B,), dtype=torch.int32, device=self.device)
+        self.cos, self.sin = rope_tables(max_ctx, 128, cfg.theta, self.device)
+        vl = lm_head.shape[0] if lm_head is not None else 0
+        self.logits_local = torch.zeros((B, vl), **f16) if vl else None
+        self.logits = torch.zeros((B, vl * world), **f16) if vl and world > 1 else self.logits_local
+        self.gathered = torch.zeros((world, B, vl), **f16) if vl and world > 1 else None
+        self.graph = None
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ kernel calls
+    def _check(self, rc):
+        if rc:
+            raise _lib.B200Error(rc, _lib.last_error())
+
+    def _matmul(self, x, w, y, n, k, sp):
+        self._check(self.L.b200_q4f16_matmul(x.data_ptr(), w[0].data_ptr(), w[1].data_ptr(), y.data_ptr(), self.batch, n, k, sp))
+
+    def _allreduce(self, t):
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+
+    def layer_step(self, i: int, delta, sp: int):
+        """One layer; `delta` is the tensor still to be added to the residual stream (or None)."""
+        cfg, L, B, w = self.cfg, self.L, self.batch, self.layers[i]
+        H, hl, il = cfg.hidden, cfg.hidden // self.world, w["inter_local"]
+        self._check(L.b200_rmsnorm(self.x.data_ptr(), delta.data_ptr() if delta is not None else None, w["norm1"].data_ptr(),
+                                   self.h.data_ptr(), B, H, cfg.eps, sp))
+        self._matmul(self.h, w["qkv"], self.qkv, 3 * hl, H, sp)
+        self._check(L.b200_rope_kv_append(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
+                                          self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), B, self.nh_local,
+                                          self.max_ctx, sp))
+        self._check(L.b200_attn_decode(self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.pos.data_ptr(),
+                                       self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
+        self._matmul(self.attn, w["o"], self.o, H, hl, sp)
+        self._allreduce(self.o)
+        self._check(L.b200_rmsnorm(self.x.data_ptr(), self.o.data_ptr(), w["norm2"].data_ptr(), self.h.data_ptr(), B, H,
+                                   cfg.eps, sp))
+        self._matmul(self.h, w["gu"], self.gu, 2 * il, H, sp)
+        self._check(L.b200_silu_mul(self.gu.data_ptr(), self.act.data_ptr(), B, il, sp))
+        self._matmul(self.act, w["down"], self.down, H, il, sp)
+        self._allreduce(self.down)
+        return self.down
+
+    def step(self):
+        """One decode step on the current stream: embeds self.tokens, runs every layer at position
+        self.pos, writes logits (when there is an lm_head), samples greedily into self.tokens and
+        advances self.pos.  All inputs live on the device, so the step can be captured and replayed."""
+        cfg, L, B = self.cfg, self.L, self.batch
+        sp = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(L.b200_embed_rows(self.embed.data_ptr(), self.tokens.data_ptr(), self.x.data_ptr(), B, cfg.hidden,
+                                      self.embed.shape[0], sp))
+        delta = None
+        for i in range(len(self.layers)):
+            delta = self.layer_step(i, delta, sp)
+        self._check(L.b200_rmsnorm(self.x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                   self.final_norm.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.eps, sp))
+        if self.lm_head is not None:
+            torch.matmul(self.h, self.lm_head.t(), out=self.logits_local)
+            if self.world > 1:
+                # gather the vocabulary slices: [world, B, V_l] -> [B, world * V_l]
+                torch.distributed.all_gather_into_tensor(self.gathered, self.logits_local, group=self.group)
+                self.logits.view(B, self.world, -1).copy_(self.gathered.permute(1, 0, 2))
+            self.tokens.copy_(torch.argmax(self.logits, dim=1).to(torch.int32))
+        self._check(L.b200_advance_pos(self.pos.data_ptr(), 1, sp))
+
+    def kernels_per_step(self) -> int:
+        """Kernels of this library launched by one step (embed + per layer 11 + final norm + advance)."""
+        return 1 + len(self.layers) * 11 + 1 + 1
+
+    def capture(self, stream):
+        """Captures one step into a CUDA graph on `stream` (after one eager warm-up step, which
+        also lets NCCL set up its channels outside the capture)."""
+        with torch.cuda.stream(stream):
+            pos0 = int(self.pos.item())
+            tok0 = self.tokens.clone()
+            self.step()
+            stream.synchronize()
+            self.pos.fill_(pos0)
+            self.tokens.copy_(tok0)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=stream):
+                self.step()
+            self.pos.fill_(pos0)
+            self.tokens.copy_(tok0)
+        return self.graph
+
+    def set_position(self, pos: int):
+        self.pos.fill_(int(pos))

@@ -1,0 +1,196 @@
+"""GPU parity of the decode-step glue kernels and of whole decoder layers against the numpy oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import decoder as odec
+from relax_b200 import _lib, decoder, tp
+
+pytestmark = pytest.mark.gpu
+
+F16 = np.float16
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def close(a, b, rtol, atol, what):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    err = np.abs(a - b)
+    bound = atol + rtol * np.abs(b)
+    i = np.argmax(err - bound)
+    assert (err <= bound).all(), f"{what}: |a-b|={err.ravel()[i]:.3e} > {bound.ravel()[i]:.3e} (a={a.ravel()[i]}, b={b.ravel()[i]})"
+
+
+@pytest.mark.parametrize("B,H", [(1, 4096), (3, 512), (16, 4096), (5, 11008)])
+def test_rmsnorm(cuda_lib, B, H):
+    rng = np.random.default_rng(B + H)
+    x = rng.standard_normal((B, H)).astype(F16)
+    d = rng.standard_normal((B, H)).astype(F16)
+    w = (1 + 0.1 * rng.standard_normal(H)).astype(F16)
+    tx, td, tw = dev(x), dev(d), dev(w)
+    ty = torch.empty_like(tx)
+    # without and with the fused residual add
+    assert cuda_lib.b200_rmsnorm(tx.data_ptr(), None, tw.data_ptr(), ty.data_ptr(), B, H, 1e-5, 0) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    close(ty.cpu().numpy(), odec.rmsnorm(x, w, 1e-5), 2e-3, 1e-4, "rmsnorm")
+    assert cuda_lib.b200_rmsnorm(tx.data_ptr(), td.data_ptr(), tw.data_ptr(), ty.data_ptr(), B, H, 1e-5, 0) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    xs = odec.add_f16(x, d)
+    assert (tx.cpu().numpy().view(np.uint16) == xs.view(np.uint16)).all(), "residual stream must be fp16(x + delta) exactly"
+    close(ty.cpu().numpy(), odec.rmsnorm(xs, w, 1e-5), 2e-3, 1e-4, "add+rmsnorm")
+
+
+def test_rmsnorm_rejects_bad_sizes(cuda_lib):
+    t = torch.zeros(64, dtype=torch.float16, device="cuda")
+    assert cuda_lib.b200_rmsnorm(t.data_ptr(), None, t.data_ptr(), t.data_ptr(), 1, 12, 1e-5, 0) == _lib.EINVAL
+    assert cuda_lib.b200_rmsnorm(None, None, t.data_ptr(), t.data_ptr(), 1, 64, 1e-5, 0) == _lib.EINVAL
+
+
+@pytest.mark.parametrize("B,I", [(1, 11008), (4, 256), (16, 1376)])
+def test_silu_mul(cuda_lib, B, I):
+    rng = np.random.default_rng(I)
+    gu = (2 * rng.standard_normal((B, 2 * I))).astype(F16)
+    tg = dev(gu)
+    out = torch.empty((B, I), dtype=torch.float16, device="cuda")
+    assert cuda_lib.b200_silu_mul(tg.data_ptr(), out.data_ptr(), B, I, 0) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    close(out.cpu().numpy(), odec.silu_mul(gu), 2e-3, 1e-4, "silu_mul")
+
+
+@pytest.mark.parametrize("B,nh,ctx,max_ctx", [(1, 32, 1024, 1024), (2, 4, 1, 64), (3, 8, 129, 300), (1, 2, 2048, 2048)])
+def test_rope_append_attention(cuda_lib, B, nh, ctx, max_ctx):
+    rng = np.random.default_rng(ctx)
+    D = 128
+    pos = ctx - 1
+    kc = np.zeros((B, max_ctx, nh, D), F16)
+    vc = np.zeros((B, max_ctx, nh, D), F16)
+    kc[:, :pos] = rng.standard_normal((B, pos, nh, D)).astype(F16)
+    vc[:, :pos] = rng.standard_normal((B, pos, nh, D)).astype(F16)
+    qkv = rng.standard_normal((B, 3 * nh * D)).astype(F16)
+    cos, sin = odec.rope_tables(max_ctx, D)
+    tq, tk, tv = dev(qkv), dev(kc), dev(vc)
+    tcos, tsin = dev(cos), dev(sin)
+    tpos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    q_out = torch.empty((B, nh, D), dtype=torch.float16, device="cuda")
+    assert cuda_lib.b200_rope_kv_append(tq.data_ptr(), tcos.data_ptr(), tsin.data_ptr(), tpos.data_ptr(), q_out.data_ptr(),
+                                        tk.data_ptr(), tv.data_ptr(), B, nh, max_ctx, 0) == 0, _lib.last_error()
+    # oracle
+    q = odec.rope(qkv[:, :nh * D].reshape(B, nh, D), cos[pos], sin[pos])
+    k = odec.rope(qkv[:, nh * D:2 * nh * D].reshape(B, nh, D), cos[pos], sin[pos])
+    kc[:, pos] = k
+    vc[:, pos] = qkv[:, 2 * nh * D:].reshape(B, nh, D)
+    torch.cuda.synchronize()
+    close(q_out.cpu().numpy(), q, 2e-3, 2e-3, "rope q")
+    close(tk.cpu().numpy()[:, pos], k, 2e-3, 2e-3, "rope k in cache")
+    assert (tv.cpu().numpy()[:, pos].view(np.uint16) == vc[:, pos].view(np.uint16)).all(), "v is copied verbatim"
+    assert (tk.cpu().numpy()[:, :pos].view(np.uint16) == kc[:, :pos].view(np.uint16)).all(), "older cache entries untouched"
+    # attention over the cache as the kernel left it
+    nbytes = cuda_lib.b200_attn_decode_scratch_bytes(B, nh, max_ctx)
+    scratch = torch.empty(nbytes // 4, dtype=torch.float32, device="cuda")
+    out = torch.empty((B, nh * D), dtype=torch.float16, device="cuda")
+    assert cuda_lib.b200_attn_decode(q_out.data_ptr(), tk.data_ptr(), tv.data_ptr(), tpos.data_ptr(), out.data_ptr(),
+                                     scratch.data_ptr(), B, nh, max_ctx, 0) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    ref = odec.attention_decode(q_out.cpu().numpy(), tk.cpu().numpy(), tv.cpu().numpy(), ctx)
+    close(out.cpu().numpy(), ref, 4e-3, 2e-3, "attention")
+
+
+def test_embed_and_advance(cuda_lib):
+    rng = np.random.default_rng(0)
+    table = rng.standard_normal((50, 256)).astype(F16)
+    ids = np.array([3, 49, 0, 7, 999, -4], dtype=np.int32)       # out-of-range ids are clamped
+    tt, ti = dev(table), dev(ids)
+    out = torch.empty((6, 256), dtype=torch.float16, device="cuda")
+    assert cuda_lib.b200_embed_rows(tt.data_ptr(), ti.data_ptr(), out.data_ptr(), 6, 256, 50, 0) == 0, _lib.last_error()
+    pos = torch.tensor([41], dtype=torch.int32, device="cuda")
+    assert cuda_lib.b200_advance_pos(pos.data_ptr(), 1, 0) == 0
+    torch.cuda.synchronize()
+    assert (out.cpu().numpy().view(np.uint16) == table[np.clip(ids, 0, 49)].view(np.uint16)).all()
+    assert int(pos.item()) == 42
+
+
+SMALL = decoder.DecoderConfig(hidden=512, heads=4, inter=768, layers=2, vocab=1000)
+
+
+def oracle_steps(cfg, layers, embed, final_norm, lm_head, tokens, steps, max_ctx, start_pos=0):
+    """Greedy decode with the numpy oracle; returns per-step (hidden after final norm, logits)."""
+    B = len(tokens)
+    D = cfg.head_dim
+    cos, sin = odec.rope_tables(max_ctx, D, cfg.theta)
+    kc = [np.zeros((B, max_ctx, cfg.heads, D), F16) for _ in layers]
+    vc = [np.zeros((B, max_ctx, cfg.heads, D), F16) for _ in layers]
+    out = []
+    tok = np.array(tokens)
+    for s in range(steps):
+        x = embed[tok]
+        delta = None
+        for i, w in enumerate(layers):
+            x, delta = odec.layer_decode(x, delta, w, kc[i], vc[i], start_pos + s, cos, sin, cfg.heads, cfg.eps)
+        x = odec.add_f16(x, delta)
+        h = odec.rmsnorm(x, final_norm, cfg.eps)
+        logits = (h.astype(np.float32) @ lm_head.astype(np.float32).T).astype(F16)
+        out.append((h, logits))
+        tok = np.argmax(logits.astype(np.float32), axis=1)
+    return out
+
+
+@pytest.mark.parametrize("B", [1, 3])
+def test_decoder_steps_match_oracle(cuda_lib, B):
+    cfg = SMALL
+    rng = np.random.default_rng(11)
+    layers = [decoder.synth_layer_numpy(cfg, 100 + i) for i in range(cfg.layers)]
+    embed = (0.5 * rng.standard_normal((cfg.vocab, cfg.hidden))).astype(F16)
+    final_norm = np.ones(cfg.hidden, F16)
+    lm_head = (0.05 * rng.standard_normal((cfg.vocab, cfg.hidden))).astype(F16)
+    tokens = list(rng.integers(0, cfg.vocab, B))
+    max_ctx, steps = 32, 3
+    ref = oracle_steps(cfg, layers, embed, final_norm, lm_head, tokens, steps, max_ctx)
+
+    shards = [decoder.to_device(tp.shard_layer(l, 0, 1, cfg.hidden, cfg.inter), "cuda") for l in layers]
+    eng = decoder.DecodeEngine(cfg, shards, dev(embed), dev(final_norm), dev(lm_head), B, max_ctx, "cuda")
+    eng.tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
+    for s in range(steps):
+        # feed the oracle's token choice so that a near-tie in the logits cannot fork the two runs
+        if s > 0:
+            eng.tokens.copy_(torch.from_numpy(np.argmax(ref[s - 1][1].astype(np.float32), axis=1).astype(np.int32)))
+        eng.step()
+        torch.cuda.synchronize()
+        h = eng.h.cpu().numpy()
+        scale = np.abs(ref[s][0].astype(np.float32)).max()
+        close(h, ref[s][0], 1e-2, 1e-2 * scale, f"hidden state at step {s}")
+        lscale = np.abs(ref[s][1].astype(np.float32)).max()
+        close(eng.logits.cpu().numpy(), ref[s][1], 1e-2, 1e-2 * lscale, f"logits at step {s}")
+    assert int(eng.pos.item()) == steps
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+def test_decoder_graph_replay_matches_eager(cuda_lib):
+    cfg = SMALL
+    rng = np.random.default_rng(5)
+    layers = [decoder.to_device(tp.shard_layer(decoder.synth_layer_numpy(cfg, 7 + i), 0, 1, cfg.hidden, cfg.inter), "cuda")
+              for i in range(cfg.layers)]
+    embed = dev((0.5 * rng.standard_normal((cfg.vocab, cfg.hidden))).astype(F16))
+    lm_head = dev((0.05 * rng.standard_normal((cfg.vocab, cfg.hidden))).astype(F16))
+    fn = dev(np.ones(cfg.hidden, F16))
+    runs = []
+    for use_graph in (False, True):
+        eng = decoder.DecodeEngine(cfg, layers, embed, fn, lm_head, 2, 16, "cuda")
+        eng.tokens.copy_(torch.tensor([5, 900], dtype=torch.int32))
+        stream = torch.cuda.Stream()
+        if use_graph:
+            eng.capture(stream)
+        toks = []
+        with torch.cuda.stream(stream):
+            for _ in range(4):
+                eng.graph.replay() if use_graph else eng.step()
+                stream.synchronize()
+                toks.append(eng.tokens.cpu().numpy().copy())
+        runs.append((toks, eng.logits.cpu().numpy().copy(), int(eng.pos.item())))
+    assert runs[0][2] == runs[1][2] == 4
+    for a, b in zip(runs[0][0], runs[1][0]):
+        assert (a == b).all()
+    assert (runs[0][1].view(np.uint16) == runs[1][1].view(np.uint16)).all(), "graph replay must reproduce the eager step bit for bit"
