@@ -189,6 +189,101 @@ def run_reference(args):
     return 0
 
 
+# ------------------------------------------------------------------------------------------ decode (7B shape)
+def run_decode(args, world, rank, dev, batch):
+    """Tokens/s of a 32-layer 7B-shaped random-init q4f16 decoder at context 2048, tensor-parallel over
+    `world` GPUs (column-/row-parallel matmuls, NCCL all-reduce after o and down).  One CUDA graph per
+    token.  Returns a dict (rank 0) with the device-resident and the end-to-end figure."""
+    import torch
+    import torch.distributed as dist
+
+    from relax_b200 import decoder, tp
+
+    cfg = decoder.DecoderConfig()
+    steps, warmup = args.decode_steps, 3
+    ctx = 2048
+    max_ctx = ctx
+    start = ctx - steps - warmup - 2 * (steps + warmup) - 2   # room for the graph, eager and e2e passes
+    layers = []
+    for i in range(cfg.layers):
+        full = decoder.synth_layer_torch(cfg, 1000 + i, dev)
+        layers.append(tp.shard_layer(full, rank, world, cfg.hidden, cfg.inter))
+        del full
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    embed = (0.02 * torch.randn((cfg.vocab, cfg.hidden), device=dev, generator=gen)).to(torch.float16)
+    vl = cfg.vocab // world
+    lm_head = embed[rank * vl:(rank + 1) * vl].contiguous()      # tied fp16 head, vocabulary-sharded
+    final_norm = torch.ones(cfg.hidden, dtype=torch.float16, device=dev)
+    eng = decoder.DecodeEngine(cfg, layers, embed, final_norm, lm_head, batch, max_ctx, dev, rank, world)
+    for kc, vc in zip(eng.kc, eng.vc):                            # a full context of N(0,1) keys and values
+        kc.normal_(generator=gen)
+        vc.normal_(generator=gen)
+    eng.tokens.copy_(torch.arange(batch, dtype=torch.int32, device=dev) % cfg.vocab)
+    eng.set_position(start)
+    torch.cuda.synchronize(dev)
+    stream = torch.cuda.Stream(device=dev)
+    eng.capture(stream)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(n):
+                fn()
+            e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            eng.graph.replay()
+    ms = timed(eng.graph.replay, steps)
+    # end to end: the host feeds the token ids of every step and reads the sampled ids back
+    tok_host = torch.zeros((batch,), dtype=torch.int32).pin_memory()
+
+    def e2e_step():
+        eng.tokens.copy_(tok_host, non_blocking=True)
+        eng.graph.replay()
+        tok_host.copy_(eng.tokens, non_blocking=True)
+        stream.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            e2e_step()
+    ms_e2e = timed(e2e_step, steps)
+    end_pos = int(eng.pos.item())
+    # weights + KV + lm_head actually read per token by one rank
+    wbytes = sum(a.numel() * a.element_size() for l in layers for k in ("qkv", "o", "gu", "down") for a in l[k])
+    kvbytes = 2 * cfg.layers * batch * end_pos * eng.nh_local * 128 * 2
+    per_rank = wbytes + kvbytes + lm_head.numel() * 2
+    out = {
+        "metric": "7B-shape decode tokens/s", "batch": batch, "context": end_pos, "tp": world,
+        "value": batch * steps / (ms * 1e-3), "unit": "tokens/s", "ms_per_token_step": ms / steps,
+        "e2e": {"value": batch * steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
+                "d2h_bytes_per_step": 4 * batch},
+        "bytes_per_step_per_gpu": per_rank,
+        "hbm_frac_of_measured": per_rank / (ms / steps * 1e-3) / 1e9 / measured_peaks()["hbm_gbs"],
+        "kernels_per_step": eng.kernels_per_step(), "lm_head": "fp16, tied to the embedding, vocabulary-sharded (library GEMM)",
+        "allreduce": "NCCL fp16, 2 per layer" if world > 1 else None, "steps": steps,
+    }
+    del eng, layers
+    torch.cuda.empty_cache()
+    return out
+
+
 # ------------------------------------------------------------------------------------------ GPU arm
 def run_gpu(args):
     import torch
@@ -286,6 +381,12 @@ def run_gpu(args):
     if err:
         raise RuntimeError(f"device error flags {err:#x}")
 
+    decode = None
+    if args.workload == "gemv" and not args.no_decode:
+        del weights, ys
+        torch.cuda.empty_cache()
+        decode = [run_decode(args, world, rank, dev, b) for b in args.decode_batches]
+
     ms_per_step = ms_total / args.steps
     us_per_launch = ms_per_step * 1e3 / copies
     if args.workload == "gemv":
@@ -332,6 +433,8 @@ def run_gpu(args):
                     "d2h_bytes_per_step": copies * m * n * 2},
             "gpu_launches": launches, "clocks": clocks,
         }
+        if decode is not None:
+            line["decode"] = decode
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -349,6 +452,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--shape", default=None, help="M,N,K override (profiling of other shapes of the same kernels)")
     ap.add_argument("--no-graph", action="store_true", help="launch directly instead of replaying a CUDA graph")
+    ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shaped decode measurement")
+    ap.add_argument("--decode-steps", type=int, default=32, help="timed tokens per sequence of the decode measurement")
+    ap.add_argument("--decode-batches", type=lambda v: [int(x) for x in v.split(",")], default=[1],
+                    help="batch sizes of the decode measurement, e.g. 1,16")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"gemv": 1000, "prefill": 100}[args.workload] if args.impl == "b200" else 10

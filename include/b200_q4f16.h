@@ -135,6 +135,20 @@ B200_API int32_t b200_q4f16_matmul_packed(void* args, int* type_codes, int num_a
 B200_API int32_t b200_q4f16_dequantize_packed(void* args, int* type_codes, int num_args, void* out_value,
                                      int* out_type_code, void* resource_handle);
 
+/* ---- skinny matmul with a neighbour of the decoder layer fused in (1 <= M <= 16, K % 256 == 0,
+ * scales 16-byte aligned).  The reference reaches the same effect when FuseOps folds elementwise
+ * producers/consumers into the matmul group (src/relay/analysis/graph_partitioner.cc:285-296).
+ *
+ * gemv_rmsnorm:  r = fp16(x + delta)  (delta may be NULL);  if x_out != NULL, x_out = r (the updated
+ *                residual stream; must not alias x);  y = (r * rsqrt(mean(r^2) + eps) * norm_w) . W^T
+ * gemv_swiglu:   gu fp16 [M, 2K] = gate | up;  y = (silu(gate) * up) . W^T
+ * Statistics and products in fp32, one fp16 rounding of the activation, as the stand-alone kernels. */
+B200_API int b200_q4f16_gemv_rmsnorm(const void* x, const void* delta, const void* norm_w, void* x_out, float eps,
+                                     const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                                     void* cuda_stream);
+B200_API int b200_q4f16_gemv_swiglu(const void* gu, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
+                                    int64_t K, void* cuda_stream);
+
 /* ---- glue kernels of a decode step (around the quantised matmuls) --------------------------
  * The reference has no RMSNorm / RoPE / attention op; these compute the composition of its
  * elementwise ops (mean, sqrt, divide, multiply, softmax, silu: python/tvm/relax/transform/

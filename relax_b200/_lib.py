@@ -61,6 +61,8 @@ PROTOTYPES = {
     "b200_q4f16_dequantize_dl": (_ci, [_dlp, _dlp, _dlp]),
     "b200_q4f16_matmul_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_dequantize_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
+    "b200_q4f16_gemv_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_gemv_swiglu": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _vp]),
     "b200_rope_kv_append": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_scratch_bytes": (_i64, [_i64, _i64, _i64]),

@@ -236,6 +236,43 @@ int b200_q4f16_gemm(const void* x, const void* wq, const void* scales, void* y, 
   return matmul_impl(kGemm, "q4f16_gemm", x, wq, scales, y, M, N, K, stream);
 }
 
+int b200_q4f16_gemv_rmsnorm(const void* x, const void* delta, const void* norm_w, void* x_out, float eps, const void* wq,
+                            const void* scales, void* y, int64_t M, int64_t N, int64_t K, void* stream) {
+  const char* who = "q4f16_gemv_rmsnorm";
+  int rc = check_matmul(who, x, wq, scales, y, M, N, K);
+  if (rc) return rc;
+  if (M < 1 || M > 16) return fail(B200_EINVAL, "%s: takes 1 <= M <= 16, got %lld", who, (long long)M);
+  if (N < 1 || K < 256 || K % 256 != 0) return fail(B200_EINVAL, "%s: needs N >= 1 and K a positive multiple of 256", who);
+  if (!aligned16(scales)) return fail(B200_EINVAL, "%s: scales must be 16-byte aligned", who);
+  if (!norm_w || !aligned16(norm_w)) return fail(B200_EINVAL, "%s: norm weight must be non-null and 16-byte aligned", who);
+  if ((delta && !aligned16(delta)) || (x_out && !aligned16(x_out))) return fail(B200_EINVAL, "%s: delta / x_out must be 16-byte aligned", who);
+  if (x_out == x) return fail(B200_EINVAL, "%s: x_out must not alias x (other CTAs still read x)", who);
+  rc = ensure_device();
+  if (rc) return rc;
+  rc = launch_gemv_pipe_rmsnorm(static_cast<const __half*>(x), static_cast<const __half*>(delta), static_cast<const __half*>(norm_w),
+                                static_cast<__half*>(x_out), eps, static_cast<const uint32_t*>(wq),
+                                static_cast<const __half*>(scales), static_cast<__half*>(y), M, N, K,
+                                static_cast<cudaStream_t>(stream));
+  if (rc == B200_ENOTREADY) return fail(B200_EINVAL, "%s: shape outside the fused kernel's domain", who);
+  return rc;
+}
+
+int b200_q4f16_gemv_swiglu(const void* gu, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                           void* stream) {
+  const char* who = "q4f16_gemv_swiglu";
+  int rc = check_matmul(who, gu, wq, scales, y, M, N, K);
+  if (rc) return rc;
+  if (M < 1 || M > 16) return fail(B200_EINVAL, "%s: takes 1 <= M <= 16, got %lld", who, (long long)M);
+  if (N < 1 || K < 256 || K % 256 != 0) return fail(B200_EINVAL, "%s: needs N >= 1 and K a positive multiple of 256", who);
+  if (!aligned16(scales)) return fail(B200_EINVAL, "%s: scales must be 16-byte aligned", who);
+  rc = ensure_device();
+  if (rc) return rc;
+  rc = launch_gemv_pipe_swiglu(static_cast<const __half*>(gu), static_cast<const uint32_t*>(wq), static_cast<const __half*>(scales),
+                               static_cast<__half*>(y), M, N, K, static_cast<cudaStream_t>(stream));
+  if (rc == B200_ENOTREADY) return fail(B200_EINVAL, "%s: shape outside the fused kernel's domain", who);
+  return rc;
+}
+
 int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, const void* scales, void* y_dev,
                            void* y_host, int64_t M, int64_t N, int64_t K, void* stream) {
   if (M < 0 || N < 0 || K < 0) return fail(B200_EINVAL, "q4f16_matmul_host: negative size");

@@ -147,22 +147,49 @@ attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restric
   const int64_t tok_stride = (int64_t)nh * 128;
   const __half* kb = k_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
   const __half* vb = v_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
-  for (int t = t0 + warp; t < t1; t += 4) {
-    uint2 kv = *reinterpret_cast<const uint2*>(kb + t * tok_stride);
-    uint2 vv = *reinterpret_cast<const uint2*>(vb + t * tok_stride);
-    const __half2* kh = reinterpret_cast<const __half2*>(&kv);
-    float2 k01 = __half22float2(kh[0]), k23 = __half22float2(kh[1]);
-    float s = qf[0] * k01.x + qf[1] * k01.y + qf[2] * k23.x + qf[3] * k23.y;
-    s = warp_sum(s);                                 // log2-domain score
-    const float mn = fmaxf(m, s);
-    const float corr = exp2f(m - mn), p = exp2f(s - mn);
-    const __half2* vh = reinterpret_cast<const __half2*>(&vv);
-    float2 v01 = __half22float2(vh[0]), v23 = __half22float2(vh[1]);
-    l = l * corr + p;
-    acc[0] = acc[0] * corr + p * v01.x;
-    acc[1] = acc[1] * corr + p * v01.y;
-    acc[2] = acc[2] * corr + p * v23.x;
-    acc[3] = acc[3] * corr + p * v23.y;
+  // Eight tokens per round: all sixteen loads are issued before the first use (a single query has
+  // no other parallelism to cover the memory latency), then one online-softmax update per round.
+  constexpr int kTok = 8;
+  for (int tb = t0 + warp * kTok; tb < t1; tb += 4 * kTok) {
+    uint2 kv[kTok], vv[kTok];
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      const int t = min(tb + j, t1 - 1);             // clamped: a token past the end is loaded but not used
+      kv[j] = *reinterpret_cast<const uint2*>(kb + t * tok_stride);
+      vv[j] = *reinterpret_cast<const uint2*>(vb + t * tok_stride);
+    }
+    float s[kTok];
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      const __half2* kh = reinterpret_cast<const __half2*>(&kv[j]);
+      const float2 k01 = __half22float2(kh[0]), k23 = __half22float2(kh[1]);
+      s[j] = qf[0] * k01.x + qf[1] * k01.y + qf[2] * k23.x + qf[3] * k23.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int j = 0; j < kTok; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
+    float mn = m;
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      if (tb + j >= t1) s[j] = -INFINITY;            // log2-domain scores; masked tokens get weight 0
+      mn = fmaxf(mn, s[j]);
+    }
+    const float corr = exp2f(m - mn);                // m = -inf on the first round: exp2f(-inf) = 0
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      const float pj = exp2f(s[j] - mn);
+      const __half2* vh = reinterpret_cast<const __half2*>(&vv[j]);
+      const float2 v01 = __half22float2(vh[0]), v23 = __half22float2(vh[1]);
+      l += pj;
+      acc[0] += pj * v01.x;
+      acc[1] += pj * v01.y;
+      acc[2] += pj * v23.x;
+      acc[3] += pj * v23.y;
+    }
     m = mn;
   }
   if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }

@@ -60,6 +60,45 @@ __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Eight fp16 at a time, fp32 inside, one round-to-nearest at the end (the same arithmetic as the
+// stand-alone RMSNorm and SwiGLU kernels).
+__device__ __forceinline__ uint4 add_f16x8(const uint4& a, const uint4& b) {
+  uint4 o;
+  const __half2* x = reinterpret_cast<const __half2*>(&a);
+  const __half2* y = reinterpret_cast<const __half2*>(&b);
+  __half2* r = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(x[j]), g = __half22float2(y[j]);
+    r[j] = __floats2half2_rn(f.x + g.x, f.y + g.y);
+  }
+  return o;
+}
+__device__ __forceinline__ uint4 scale_f16x8(const uint4& a, float inv, const uint4& w) {
+  uint4 o;
+  const __half2* x = reinterpret_cast<const __half2*>(&a);
+  const __half2* y = reinterpret_cast<const __half2*>(&w);
+  __half2* r = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(x[j]), g = __half22float2(y[j]);
+    r[j] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+  }
+  return o;
+}
+__device__ __forceinline__ uint4 silu_mul_f16x8(const uint4& gate, const uint4& up) {
+  uint4 o;
+  const __half2* x = reinterpret_cast<const __half2*>(&gate);
+  const __half2* y = reinterpret_cast<const __half2*>(&up);
+  __half2* r = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 g = __half22float2(x[j]), u = __half22float2(y[j]);
+    r[j] = __floats2half2_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+  }
+  return o;
+}
+
 // Layout of the staged x block: one 16-byte slot per (8-k word jw, batch column).  Lane (g,t)
 // reads column g of words 32c + 8t + i (i = 0..7), so the four lanes t of a row-group read
 // words 8 apart in the same instruction and their slots must differ mod 8:
@@ -77,6 +116,8 @@ struct XLayout {
   __host__ __device__ static constexpr size_t bytes(int k) { return (size_t)(k / 256) * kSlotsPerChunk * 16; }
 };
 
+enum { kPrologueNone = 0, kPrologueRmsNorm = 1, kPrologueSwiGLU = 2 };
+
 struct PipeParams {
   CUtensorMap tm_w;   // uint32 {32, N, K/256}, box {32, 16, CH}, 128B swizzle
   CUtensorMap tm_s;   // fp16   {8, N, K/256},  box {8, 16, CH}
@@ -87,6 +128,12 @@ struct PipeParams {
   int nstages;
   int ntiles;      // ceil(N / 16)
   int tiles_per_cta;
+  // what the staging of x applies on the way in (the neighbours of the matmul in a decoder layer)
+  int prologue;              // kPrologueNone / kPrologueRmsNorm / kPrologueSwiGLU
+  const __half* delta;       // RmsNorm: added to x first (or null)
+  const __half* norm_w;      // RmsNorm: weight [K]
+  __half* x_out;             // RmsNorm: fp16(x + delta) is written here by CTA 0 (or null)
+  float eps;
 };
 
 // Shared memory carve-up (after rounding the base up to 1024 bytes):
@@ -284,6 +331,39 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   uint32_t round = 0;                            // how many times the ring has wrapped
   int rb = 0;                                    // reduction buffer of the current tile
   uint32_t rround = 0;
+  // ---- RMSNorm prologue: r = fp16(x + delta), inv[m] = rsqrt(mean(r^2) + eps) for every row ------
+  // Every CTA computes the statistics itself (K values per row: nothing next to its share of W);
+  // CTA 0 also writes r out as the updated residual stream.
+  __shared__ float s_part[16][CW];
+  __shared__ float s_inv[16];
+  if (p.prologue == kPrologueRmsNorm) {
+    for (int m = 0; m < p.M; ++m) {
+      float ss = 0.f;
+      for (int k = tid * 8; k < p.K; k += kConsumers * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
+        if (p.delta) v = add_f16x8(v, *reinterpret_cast<const uint4*>(p.delta + (int64_t)m * p.K + k));
+        if (p.x_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(p.x_out + (int64_t)m * p.K + k) = v;
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_part[m][warp] = ss;
+    }
+    bar_sync(1, kConsumers);
+    if (tid < p.M) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < CW; ++w2) tot += s_part[tid][w2];
+      s_inv[tid] = rsqrtf(tot / (float)p.K + p.eps);
+    }
+    bar_sync(1, kConsumers);
+  }
+
   for (int kb = 0; kb < nkb; ++kb) {
     const int k_lo = kb * p.kblk;
     const int k_hi = min(p.K, k_lo + p.kblk);
@@ -295,7 +375,20 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         int j = i / NC, m = i - j * NC;
         int k = k_lo + j * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (m < p.M && k < p.K) v = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
+        if (m < p.M && k < p.K) {
+          if (p.prologue == kPrologueSwiGLU) {
+            // x is [M, 2K] = gate | up: a = silu(gate) * up, fp32 inside, one fp16 rounding
+            const uint4 g = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + k);
+            const uint4 u = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + p.K + k);
+            v = silu_mul_f16x8(g, u);
+          } else {
+            v = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
+            if (p.prologue == kPrologueRmsNorm) {
+              if (p.delta) v = add_f16x8(v, *reinterpret_cast<const uint4*>(p.delta + (int64_t)m * p.K + k));
+              v = scale_f16x8(v, s_inv[m], *reinterpret_cast<const uint4*>(p.norm_w + k));
+            }
+          }
+        }
         uint4 q;
         q.x = __byte_perm(v.x, v.z, 0x5410);
         q.y = __byte_perm(v.x, v.z, 0x7632);
@@ -387,9 +480,17 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   }
 }
 
+struct Prologue {
+  int kind = kPrologueNone;
+  const __half* delta = nullptr;
+  const __half* norm_w = nullptr;
+  __half* x_out = nullptr;
+  float eps = 0.f;
+};
+
 template <int NC, int CW, int CH>
 int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int M, int N, int K,
-                cudaStream_t stream) {
+                cudaStream_t stream, const Prologue& pro) {
   constexpr int MT = (NC + 7) / 8;
   constexpr int kOut = MT * 128;
   constexpr int KC = 256 * CH;
@@ -410,6 +511,7 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   }
   p.x = x; p.y = y;
   p.M = M; p.N = N; p.K = K;
+  p.prologue = pro.kind; p.delta = pro.delta; p.norm_w = pro.norm_w; p.x_out = pro.x_out; p.eps = pro.eps;
   p.ntiles = (N + kRows - 1) / kRows;
   const int kpad = ((K + KC - 1) / KC) * KC;
   const int stages_per_tile = kpad / KC;
@@ -490,12 +592,20 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
 
 template <int CW, int CH>
 int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int m, int n, int k,
-                  cudaStream_t stream) {
-  if (m == 1) return launch_pipe<1, CW, CH>(x, wq, scales, y, m, n, k, stream);
-  if (m == 2) return launch_pipe<2, CW, CH>(x, wq, scales, y, m, n, k, stream);
-  if (m <= 4) return launch_pipe<4, CW, CH>(x, wq, scales, y, m, n, k, stream);
-  if (m <= 8) return launch_pipe<8, CW, CH>(x, wq, scales, y, m, n, k, stream);
-  return launch_pipe<16, CW, CH>(x, wq, scales, y, m, n, k, stream);
+                  cudaStream_t stream, const Prologue& pro) {
+  if (m == 1) return launch_pipe<1, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
+  if (m == 2) return launch_pipe<2, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
+  if (m <= 4) return launch_pipe<4, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
+  if (m <= 8) return launch_pipe<8, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
+  return launch_pipe<16, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
+}
+
+int dispatch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N, int64_t K,
+                  cudaStream_t stream, const Prologue& pro) {
+  if (K % 256 != 0 || (reinterpret_cast<uintptr_t>(scales) & 15u)) return B200_ENOTREADY;
+  int m = (int)M, n = (int)N, k = (int)K;
+  if (options().gemv_warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream, pro);
+  return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream, pro);
 }
 
 }  // namespace
@@ -504,10 +614,24 @@ int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __h
 // the register-streaming kernel).
 int launch_gemv_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                      int64_t K, cudaStream_t stream) {
-  if (K % 256 != 0 || (reinterpret_cast<uintptr_t>(scales) & 15u)) return B200_ENOTREADY;
-  int m = (int)M, n = (int)N, k = (int)K;
-  if (options().gemv_warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream);
-  return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream);
+  return dispatch_pipe(x, wq, scales, y, M, N, K, stream, Prologue{});
+}
+
+// y = (rmsnorm(fp16(x + delta)) * norm_w) . decode(W)^T; fp16(x + delta) also goes to x_out (if given).
+int launch_gemv_pipe_rmsnorm(const __half* x, const __half* delta, const __half* norm_w, __half* x_out, float eps,
+                             const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N, int64_t K,
+                             cudaStream_t stream) {
+  Prologue pro;
+  pro.kind = kPrologueRmsNorm; pro.delta = delta; pro.norm_w = norm_w; pro.x_out = x_out; pro.eps = eps;
+  return dispatch_pipe(x, wq, scales, y, M, N, K, stream, pro);
+}
+
+// y = (silu(gu[:, :K]) * gu[:, K:]) . decode(W)^T
+int launch_gemv_pipe_swiglu(const __half* gu, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                            int64_t K, cudaStream_t stream) {
+  Prologue pro;
+  pro.kind = kPrologueSwiGLU;
+  return dispatch_pipe(gu, wq, scales, y, M, N, K, stream, pro);
 }
 
 int gemv_pipe_error_read_and_clear() {

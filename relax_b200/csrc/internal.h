@@ -30,6 +30,13 @@ int launch_dequantize(const uint32_t* wq, const __half* scales, __half* w, int64
                       cudaStream_t stream);
 int launch_gemv(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
+// Skinny matmul with a neighbour of the decoder layer fused into the staging of x (1 <= M <= 16,
+// K % 256 == 0, 16-byte aligned scales; B200_ENOTREADY otherwise).
+int launch_gemv_pipe_rmsnorm(const __half* x, const __half* delta, const __half* norm_w, __half* x_out, float eps,
+                             const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N, int64_t K,
+                             cudaStream_t stream);
+int launch_gemv_pipe_swiglu(const __half* gu, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                            int64_t K, cudaStream_t stream);
 int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
 

@@ -101,7 +101,7 @@ class DecodeEngine:
     """
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
-                 device, rank: int = 0, world: int = 1, group=None):
+                 device, rank: int = 0, world: int = 1, group=None, fused: bool = True):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
@@ -113,7 +113,11 @@ class DecodeEngine:
         f16 = dict(dtype=torch.float16, device=self.device)
         hl = H // world
         il_max = max(l["inter_local"] for l in layers) if layers else cfg.inter
+        # fused: RMSNorm (+ residual add) and SwiGLU run inside the staging of the next skinny matmul
+        # (7 kernels per layer instead of 11); needs batch <= 16, the skinny kernel's range
+        self.fused = bool(fused) and B <= 16
         self.x = torch.zeros((B, H), **f16)            # residual stream
+        self.x2 = torch.zeros((B, H), **f16)           # its second buffer (fused path ping-pongs)
         self.h = torch.zeros((B, H), **f16)            # normalised activations
         self.qkv = torch.zeros((B, 3 * hl), **f16)
         self.q = torch.zeros((B, self.nh_local, 128), **f16)
@@ -149,12 +153,19 @@ class DecodeEngine:
             torch.distributed.all_reduce(t, group=self.group)
 
     def layer_step(self, i: int, delta, sp: int):
-        """One layer; `delta` is the tensor still to be added to the residual stream (or None)."""
+        """One layer; `delta` is the tensor still to be added to the residual stream (or None).
+        Returns the layer's MLP output (to be added by whoever consumes the stream next)."""
         cfg, L, B, w = self.cfg, self.L, self.batch, self.layers[i]
         H, hl, il = cfg.hidden, cfg.hidden // self.world, w["inter_local"]
-        self._check(L.b200_rmsnorm(self.x.data_ptr(), delta.data_ptr() if delta is not None else None, w["norm1"].data_ptr(),
-                                   self.h.data_ptr(), B, H, cfg.eps, sp))
-        self._matmul(self.h, w["qkv"], self.qkv, 3 * hl, H, sp)
+        dptr = delta.data_ptr() if delta is not None else None
+        if self.fused:
+            # residual stream: x --(+delta)--> x2 --(+o)--> x
+            self._check(L.b200_q4f16_gemv_rmsnorm(self.x.data_ptr(), dptr, w["norm1"].data_ptr(), self.x2.data_ptr(), cfg.eps,
+                                                  w["qkv"][0].data_ptr(), w["qkv"][1].data_ptr(), self.qkv.data_ptr(),
+                                                  B, 3 * hl, H, sp))
+        else:
+            self._check(L.b200_rmsnorm(self.x.data_ptr(), dptr, w["norm1"].data_ptr(), self.h.data_ptr(), B, H, cfg.eps, sp))
+            self._matmul(self.h, w["qkv"], self.qkv, 3 * hl, H, sp)
         self._check(L.b200_rope_kv_append(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
                                           self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), B, self.nh_local,
                                           self.max_ctx, sp))
@@ -162,11 +173,18 @@ class DecodeEngine:
                                        self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
         self._matmul(self.attn, w["o"], self.o, H, hl, sp)
         self._allreduce(self.o)
-        self._check(L.b200_rmsnorm(self.x.data_ptr(), self.o.data_ptr(), w["norm2"].data_ptr(), self.h.data_ptr(), B, H,
-                                   cfg.eps, sp))
-        self._matmul(self.h, w["gu"], self.gu, 2 * il, H, sp)
-        self._check(L.b200_silu_mul(self.gu.data_ptr(), self.act.data_ptr(), B, il, sp))
-        self._matmul(self.act, w["down"], self.down, H, il, sp)
+        if self.fused:
+            self._check(L.b200_q4f16_gemv_rmsnorm(self.x2.data_ptr(), self.o.data_ptr(), w["norm2"].data_ptr(), self.x.data_ptr(),
+                                                  cfg.eps, w["gu"][0].data_ptr(), w["gu"][1].data_ptr(), self.gu.data_ptr(),
+                                                  B, 2 * il, H, sp))
+            self._check(L.b200_q4f16_gemv_swiglu(self.gu.data_ptr(), w["down"][0].data_ptr(), w["down"][1].data_ptr(),
+                                                 self.down.data_ptr(), B, H, il, sp))
+        else:
+            self._check(L.b200_rmsnorm(self.x.data_ptr(), self.o.data_ptr(), w["norm2"].data_ptr(), self.h.data_ptr(), B, H,
+                                       cfg.eps, sp))
+            self._matmul(self.h, w["gu"], self.gu, 2 * il, H, sp)
+            self._check(L.b200_silu_mul(self.gu.data_ptr(), self.act.data_ptr(), B, il, sp))
+            self._matmul(self.act, w["down"], self.down, H, il, sp)
         self._allreduce(self.down)
         return self.down
 
@@ -193,12 +211,13 @@ class DecodeEngine:
         self._check(L.b200_advance_pos(self.pos.data_ptr(), 1, sp))
 
     def kernels_per_step(self) -> int:
-        """Kernels of this library launched by one step (embed + per layer 11 + final norm + advance)."""
-        return 1 + len(self.layers) * 11 + 1 + 1
+        """Kernels of this library launched by one step (embed + 7 or 11 per layer + final norm + advance)."""
+        return 1 + len(self.layers) * (7 if self.fused else 11) + 1 + 1
 
     def capture(self, stream):
         """Captures one step into a CUDA graph on `stream` (after one eager warm-up step, which
         also lets NCCL set up its channels outside the capture)."""
+        stream.wait_stream(torch.cuda.current_stream(self.device))   # buffers were filled on the caller's stream
         with torch.cuda.stream(stream):
             pos0 = int(self.pos.item())
             tok0 = self.tokens.clone()
@@ -211,6 +230,7 @@ class DecodeEngine:
                 self.step()
             self.pos.fill_(pos0)
             self.tokens.copy_(tok0)
+            stream.synchronize()
         return self.graph
 
     def set_position(self, pos: int):

@@ -138,8 +138,55 @@ def oracle_steps(cfg, layers, embed, final_norm, lm_head, tokens, steps, max_ctx
     return out
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (3, 300, 4096), (16, 64, 256), (8, 4096, 2816)])
+def test_gemv_with_fused_neighbours(cuda_lib, M, N, K):
+    from relax_b200 import synth
+    from util import assert_matmul_close
+
+    rng = np.random.default_rng(M * N + K)
+    _, wq, s = synth.make_case(1, N, K, seed=K + M)
+    twq, ts = dev(wq), dev(s)
+    # RMSNorm (+ residual add) prologue
+    x = rng.standard_normal((M, K)).astype(F16)
+    d = rng.standard_normal((M, K)).astype(F16)
+    w = (1 + 0.1 * rng.standard_normal(K)).astype(F16)
+    tx, td, tw = dev(x), dev(d), dev(w)
+    x_out = torch.full((M, K), float("nan"), dtype=torch.float16, device="cuda")
+    y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    for delta in (None, td):
+        assert cuda_lib.b200_q4f16_gemv_rmsnorm(tx.data_ptr(), delta.data_ptr() if delta is not None else None, tw.data_ptr(),
+                                                x_out.data_ptr(), 1e-5, twq.data_ptr(), ts.data_ptr(), y.data_ptr(), M, N, K, 0) == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        r = odec.add_f16(x, d) if delta is not None else x
+        assert (x_out.cpu().numpy().view(np.uint16) == r.view(np.uint16)).all(), "updated residual stream"
+        a = odec.rmsnorm(r, w, 1e-5)
+        # the activation may differ from the oracle's by one fp16 ulp (rsqrt vs 1/sqrt): compare against
+        # the matmul of the oracle's activation with a tolerance that covers one ulp per element
+        ref = oracle.c_matmul(a, wq, s).astype(np.float32)
+        wd = oracle.c_dequantize(wq, s).astype(np.float32)
+        slack = 2.0 ** -10 * (np.abs(a.astype(np.float32)) @ np.abs(wd).T)
+        err = np.abs(y.cpu().numpy().astype(np.float32) - ref)
+        assert (err <= 2.0 ** -9 * np.abs(ref) + 0.05 * slack + 1e-4).all(), f"gemv_rmsnorm: max err {err.max()}"
+    # aliasing x_out with x is refused
+    assert cuda_lib.b200_q4f16_gemv_rmsnorm(tx.data_ptr(), None, tw.data_ptr(), tx.data_ptr(), 1e-5, twq.data_ptr(), ts.data_ptr(),
+                                            y.data_ptr(), M, N, K, 0) == _lib.EINVAL
+    # SwiGLU prologue
+    gu = (1.5 * rng.standard_normal((M, 2 * K))).astype(F16)
+    tg = dev(gu)
+    assert cuda_lib.b200_q4f16_gemv_swiglu(tg.data_ptr(), twq.data_ptr(), ts.data_ptr(), y.data_ptr(), M, N, K, 0) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    a = odec.silu_mul(gu)
+    ref = oracle.c_matmul(a, wq, s).astype(np.float32)
+    wd = oracle.c_dequantize(wq, s).astype(np.float32)
+    slack = 2.0 ** -10 * (np.abs(a.astype(np.float32)) @ np.abs(wd).T)
+    err = np.abs(y.cpu().numpy().astype(np.float32) - ref)
+    assert (err <= 2.0 ** -9 * np.abs(ref) + 0.05 * slack + 1e-4).all(), f"gemv_swiglu: max err {err.max()}"
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("B", [1, 3])
-def test_decoder_steps_match_oracle(cuda_lib, B):
+def test_decoder_steps_match_oracle(cuda_lib, B, fused):
     cfg = SMALL
     rng = np.random.default_rng(11)
     layers = [decoder.synth_layer_numpy(cfg, 100 + i) for i in range(cfg.layers)]
@@ -151,7 +198,8 @@ def test_decoder_steps_match_oracle(cuda_lib, B):
     ref = oracle_steps(cfg, layers, embed, final_norm, lm_head, tokens, steps, max_ctx)
 
     shards = [decoder.to_device(tp.shard_layer(l, 0, 1, cfg.hidden, cfg.inter), "cuda") for l in layers]
-    eng = decoder.DecodeEngine(cfg, shards, dev(embed), dev(final_norm), dev(lm_head), B, max_ctx, "cuda")
+    eng = decoder.DecodeEngine(cfg, shards, dev(embed), dev(final_norm), dev(lm_head), B, max_ctx, "cuda", fused=fused)
+    assert eng.fused == fused
     eng.tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
     for s in range(steps):
         # feed the oracle's token choice so that a near-tie in the logits cannot fork the two runs
