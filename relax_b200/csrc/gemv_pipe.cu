@@ -337,22 +337,39 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   __shared__ float s_part[16][CW];
   __shared__ float s_inv[16];
   if (p.prologue == kPrologueRmsNorm) {
-    for (int m = 0; m < p.M; ++m) {
-      float ss = 0.f;
-      for (int k = tid * 8; k < p.K; k += kConsumers * 8) {
-        uint4 v = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
-        if (p.delta) v = add_f16x8(v, *reinterpret_cast<const uint4*>(p.delta + (int64_t)m * p.K + k));
-        if (p.x_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(p.x_out + (int64_t)m * p.K + k) = v;
-        const __half2* h = reinterpret_cast<const __half2*>(&v);
+    // four rows at a time so that eight independent loads are in flight per thread
+    constexpr int R = NC >= 8 ? 4 : 1;
+    for (int m0 = 0; m0 < p.M; m0 += R) {
+      float ss[R];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __half22float2(h[j]);
-          ss += f.x * f.x + f.y * f.y;
+      for (int r = 0; r < R; ++r) ss[r] = 0.f;
+      for (int k = tid * 8; k < p.K; k += kConsumers * 8) {
+        uint4 v[R], d[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int m = min(m0 + r, p.M - 1);
+          v[r] = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
+          if (p.delta) d[r] = *reinterpret_cast<const uint4*>(p.delta + (int64_t)m * p.K + k);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if (m0 + r >= p.M) continue;
+          if (p.delta) v[r] = add_f16x8(v[r], d[r]);
+          if (p.x_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(p.x_out + (int64_t)(m0 + r) * p.K + k) = v[r];
+          const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            ss[r] += f.x * f.x + f.y * f.y;
+          }
         }
       }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) s_part[m][warp] = ss;
+      for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], o);
+        if (lane == 0 && m0 + r < p.M) s_part[m0 + r][warp] = ss[r];
+      }
     }
     bar_sync(1, kConsumers);
     if (tid < p.M) {
@@ -370,31 +387,55 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     // ---- stage x[:, k_lo .. k_lo + kblk) permuted per 8 k; zero beyond K and beyond M --------------
     if (kb > 0) bar_sync(1, kConsumers);         // everyone is done reading the previous block
     {
+      // four items per thread and round: all loads of a round are issued before the first use
       const int words = p.kblk >> 3;
-      for (int i = tid; i < words * NC; i += kConsumers) {
-        int j = i / NC, m = i - j * NC;
-        int k = k_lo + j * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (m < p.M && k < p.K) {
-          if (p.prologue == kPrologueSwiGLU) {
-            // x is [M, 2K] = gate | up: a = silu(gate) * up, fp32 inside, one fp16 rounding
-            const uint4 g = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + k);
-            const uint4 u = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + p.K + k);
-            v = silu_mul_f16x8(g, u);
-          } else {
-            v = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
-            if (p.prologue == kPrologueRmsNorm) {
-              if (p.delta) v = add_f16x8(v, *reinterpret_cast<const uint4*>(p.delta + (int64_t)m * p.K + k));
-              v = scale_f16x8(v, s_inv[m], *reinterpret_cast<const uint4*>(p.norm_w + k));
+      const int items = words * NC;
+      constexpr int R = NC >= 8 ? 4 : 1;            // (registers: small batches keep two CTAs per SM)
+      for (int i0 = tid; i0 < items; i0 += kConsumers * R) {
+        uint4 a[R], b[R], c[R];
+        bool live[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int i = i0 + r * kConsumers;
+          const int j = i / NC, m = i - j * NC;
+          const int k = k_lo + j * 8;
+          live[r] = i < items && m < p.M && k < p.K;
+          a[r] = b[r] = c[r] = make_uint4(0, 0, 0, 0);
+          if (live[r]) {
+            if (p.prologue == kPrologueSwiGLU) {
+              // x is [M, 2K] = gate | up
+              a[r] = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + k);
+              b[r] = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + p.K + k);
+            } else {
+              a[r] = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
+              if (p.prologue == kPrologueRmsNorm) {
+                if (p.delta) b[r] = *reinterpret_cast<const uint4*>(p.delta + (int64_t)m * p.K + k);
+                c[r] = *reinterpret_cast<const uint4*>(p.norm_w + k);
+              }
             }
           }
         }
-        uint4 q;
-        q.x = __byte_perm(v.x, v.z, 0x5410);
-        q.y = __byte_perm(v.x, v.z, 0x7632);
-        q.z = __byte_perm(v.y, v.w, 0x5410);
-        q.w = __byte_perm(v.y, v.w, 0x7632);
-        xs[XLayout<NC>::slot(j, m)] = q;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int i = i0 + r * kConsumers;
+          if (i >= items) continue;
+          const int j = i / NC, m = i - j * NC;
+          uint4 v = a[r];
+          if (live[r]) {
+            if (p.prologue == kPrologueSwiGLU) {
+              v = silu_mul_f16x8(a[r], b[r]);       // fp32 inside, one fp16 rounding
+            } else if (p.prologue == kPrologueRmsNorm) {
+              if (p.delta) v = add_f16x8(v, b[r]);
+              v = scale_f16x8(v, s_inv[m], c[r]);
+            }
+          }
+          uint4 q;
+          q.x = __byte_perm(v.x, v.z, 0x5410);
+          q.y = __byte_perm(v.x, v.z, 0x7632);
+          q.z = __byte_perm(v.y, v.w, 0x5410);
+          q.w = __byte_perm(v.y, v.w, 0x7632);
+          xs[XLayout<NC>::slot(j, m)] = q;
+        }
       }
     }
     bar_sync(1, kConsumers);
