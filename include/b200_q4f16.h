@@ -175,6 +175,22 @@ B200_API int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t m
 B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
                               void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);
 
+/* Same attention for callers that cannot hand over scratch memory.  (No counterpart in the
+ * reference.)  Some hosts of this library are not allowed to allocate device memory at the point
+ * where they call it: a runtime whose memory planner has already fixed every buffer of the step,
+ * or a plugin running under a host that forbids cudaMalloc on its threads.  This entry point
+ * allocates nothing, neither here nor in anything it calls: the partial results of the two-pass
+ * attention go to a 4.26 MB array that is part of the library image on every GPU that loads it.
+ *   - Limit: B * nh * ceil(max_ctx / 128) <= 8192 (e.g. 16 sequences x 32 heads x 2048 tokens);
+ *     larger problems are refused with B200_EINVAL and a message, nothing is launched.
+ *   - The first call on each device looks up the array's device address (make that device current;
+ *     do this first call outside any stream capture).
+ *   - All calls on a device share the one array: two calls that overlap on the GPU (different
+ *     streams) overwrite each other's partial results.  Calls ordered on one stream are safe; every
+ *     slot that is read has been written by the same call, so nothing needs clearing in between. */
+B200_API int b200_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
+                                     int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);
+
 /* out[b,:] = table[ids[b],:]: fp16 table [vocab,H], int32 ids [B] on the device (ids are clamped
  * to the table).  H % 8 == 0.  (reference: relax.take, python/tvm/relax/transform/legalize_ops.py:168) */
 B200_API int b200_embed_rows(const void* table, const void* ids, void* out, int64_t B, int64_t H, int64_t vocab,

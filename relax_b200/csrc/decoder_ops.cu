@@ -370,6 +370,39 @@ int b200_advance_pos(void* pos, int64_t delta, void* stream) {
                 (int)delta);
 }
 
+// ---- attention without caller-provided scratch ------------------------------------------------
+// Partial results live in a fixed array inside the library image instead of a buffer the caller
+// allocates.  kStaticAttnSlots (batch * heads * 128-token chunks) bounds what fits.
+constexpr int64_t kStaticAttnSlots = 8192;                       // e.g. 16 sequences x 32 heads x 2048 tokens
+static __device__ __align__(256) float g_attn_static_scratch[kStaticAttnSlots * 130];   // 4.26 MB per GPU
+
+int b200_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out, int64_t B,
+                            int64_t nh, int64_t max_ctx, void* stream) {
+  if (B <= 0 || nh <= 0 || max_ctx <= 0) return fail(B200_EINVAL, "attn_decode_static: bad sizes");
+  if (!q || !k_cache || !v_cache || !pos || !out) return fail(B200_EINVAL, "attn_decode_static: null pointer");
+  const int64_t nsplit = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+  if (B * nh * nsplit > kStaticAttnSlots)
+    return fail(B200_EINVAL,
+                "attn_decode_static: batch %lld x heads %lld x %lld chunks of 128 tokens = %lld partial results, the built-in "
+                "scratch holds %lld; use b200_attn_decode with a caller-owned buffer",
+                (long long)B, (long long)nh, (long long)nsplit, (long long)(B * nh * nsplit), (long long)kStaticAttnSlots);
+  int rc = ensure_device();
+  if (rc) return rc;
+  // The array's name is only a handle on the host: its device address is looked up once per
+  // device, with that device current, and handed to the kernels like any other buffer.
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(B200_ENODEVICE, "attn_decode_static: no current device");
+  if (!scratch_of_device[dev]) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_attn_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(B200_ELAUNCH, "attn_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    scratch_of_device[dev] = ptr;
+  }
+  return b200_attn_decode(q, k_cache, v_cache, pos, out, scratch_of_device[dev], B, nh, max_ctx, stream);
+}
+
 int b200_silu_mul(const void* gu, void* out, int64_t B, int64_t I, void* stream) {
   if (B < 0 || I <= 0 || I % 8 != 0) return fail(B200_EINVAL, "silu_mul: need I %% 8 == 0");
   if (B == 0) return B200_OK;
