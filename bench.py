@@ -215,7 +215,8 @@ def run_decode(args, world, rank, dev, batch):
     vl = cfg.vocab // world
     lm_head = embed[rank * vl:(rank + 1) * vl].contiguous()      # tied fp16 head, vocabulary-sharded
     final_norm = torch.ones(cfg.hidden, dtype=torch.float16, device=dev)
-    eng = decoder.DecodeEngine(cfg, layers, embed, final_norm, lm_head, batch, max_ctx, dev, rank, world)
+    eng = decoder.DecodeEngine(cfg, layers, embed, final_norm, lm_head, batch, max_ctx, dev, rank, world,
+                               peer_reduce=not args.decode_nccl)
     for kc, vc in zip(eng.kc, eng.vc):                            # a full context of N(0,1) keys and values
         kc.normal_(generator=gen)
         vc.normal_(generator=gen)
@@ -277,7 +278,8 @@ def run_decode(args, world, rank, dev, batch):
         "bytes_per_step_per_gpu": per_rank,
         "hbm_frac_of_measured": per_rank / (ms / steps * 1e-3) / 1e9 / measured_peaks()["hbm_gbs"],
         "kernels_per_step": eng.kernels_per_step(), "lm_head": "fp16, tied to the embedding, vocabulary-sharded (library GEMM)",
-        "allreduce": "NCCL fp16, 2 per layer" if world > 1 else None, "steps": steps,
+        "allreduce": (None if world == 1 else "fused into the o/down matmul kernels over NVLink peer memory (fp16 partials, "
+                      "rank-order sum)" if eng.peer is not None else "NCCL fp16, 2 per layer"), "steps": steps,
     }
     del eng, layers
     torch.cuda.empty_cache()
@@ -453,6 +455,7 @@ def main():
     ap.add_argument("--shape", default=None, help="M,N,K override (profiling of other shapes of the same kernels)")
     ap.add_argument("--no-graph", action="store_true", help="launch directly instead of replaying a CUDA graph")
     ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shaped decode measurement")
+    ap.add_argument("--decode-nccl", action="store_true", help="tensor-parallel sums through NCCL instead of the fused kernel")
     ap.add_argument("--decode-steps", type=int, default=32, help="timed tokens per sequence of the decode measurement")
     ap.add_argument("--decode-batches", type=lambda v: [int(x) for x in v.split(",")], default=[1],
                     help="batch sizes of the decode measurement, e.g. 1,16")

@@ -149,6 +149,36 @@ B200_API int b200_q4f16_gemv_rmsnorm(const void* x, const void* delta, const voi
 B200_API int b200_q4f16_gemv_swiglu(const void* gu, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
                                     int64_t K, void* cuda_stream);
 
+/* ---- row-parallel skinny matmul with the sum over tensor-parallel ranks fused in ------------------
+ * The reference has no sharding or collective; this is the row-parallel half of the tensor-parallel
+ * layout: every rank multiplies its K slice, the partial results are added over ranks.  Here the sum
+ * is the tail of the matmul kernel itself, over NVLink peer memory, instead of a separate collective:
+ * the CTA that finishes last on a GPU publishes a flag to every peer, waits (bounded, 2 s) for theirs,
+ * then adds the `world` partial results in rank order (same bits on every rank) into `out`.
+ *
+ *   y            this rank's partial result [M,N] fp16; must be peer_y[rank], i.e. memory every peer maps
+ *   peer_y[r]    rank r's y as mapped on this GPU; peer_flags[r]: rank r's int32 flag array likewise
+ *   flag_base    first of `world` consecutive flag slots reserved for this call site
+ *   epoch        device int32 that grows by one per step; flags carry *epoch + 1, so slots are never reset
+ *   done_counter device int32, zero before the first launch (the kernel leaves it zero)
+ *   out          [M,N] fp16 local result
+ * A call site may reuse y / its flag slots in the next step only after another reduction of this kind
+ * has completed in between (two alternating call sites, as o-proj and down-proj of a decoder layer,
+ * satisfy this).  1 <= M <= 16, K % 256 == 0, N % 8 == 0, scales 16-byte aligned, world <= 8.
+ * swiglu != 0: x is gate|up [M,2K] and silu(gate)*up is applied first (see b200_q4f16_gemv_swiglu).
+ * A wait that runs out sets bit 4 of the skinny kernel's byte in b200_device_error_flags(). */
+typedef struct {
+  int32_t world, rank;
+  const void* peer_y[8];
+  void* peer_flags[8];
+  int32_t flag_base;
+  const void* epoch;
+  void* done_counter;
+  void* out;
+} B200PeerReduce;
+B200_API int b200_q4f16_gemv_allreduce(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
+                                       int64_t K, int32_t swiglu, const B200PeerReduce* red, void* cuda_stream);
+
 /* ---- glue kernels of a decode step (around the quantised matmuls) --------------------------
  * The reference has no RMSNorm / RoPE / attention op; these compute the composition of its
  * elementwise ops (mean, sqrt, divide, multiply, softmax, silu: python/tvm/relax/transform/

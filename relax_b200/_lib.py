@@ -43,6 +43,17 @@ class DLTensor(ctypes.Structure):
     ]
 
 
+class PeerReduce(ctypes.Structure):
+    """B200PeerReduce of include/b200_q4f16.h."""
+
+    _fields_ = [
+        ("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+        ("peer_y", ctypes.c_void_p * 8), ("peer_flags", ctypes.c_void_p * 8),
+        ("flag_base", ctypes.c_int32), ("epoch", ctypes.c_void_p), ("done_counter", ctypes.c_void_p),
+        ("out", ctypes.c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); one entry per prototype in include/b200_q4f16.h
 _vp, _i64, _ci = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
 _dlp = ctypes.POINTER(DLTensor)
@@ -63,6 +74,7 @@ PROTOTYPES = {
     "b200_q4f16_dequantize_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_gemv_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_gemv_swiglu": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_gemv_allreduce": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int32, ctypes.POINTER(PeerReduce), _vp]),
     "b200_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _vp]),
     "b200_rope_kv_append": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_scratch_bytes": (_i64, [_i64, _i64, _i64]),

@@ -273,6 +273,35 @@ int b200_q4f16_gemv_swiglu(const void* gu, const void* wq, const void* scales, v
   return rc;
 }
 
+int b200_q4f16_gemv_allreduce(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                              int32_t swiglu, const B200PeerReduce* red, void* stream) {
+  const char* who = "q4f16_gemv_allreduce";
+  int rc = check_matmul(who, x, wq, scales, y, M, N, K);
+  if (rc) return rc;
+  if (M < 1 || M > 16) return fail(B200_EINVAL, "%s: takes 1 <= M <= 16, got %lld", who, (long long)M);
+  if (N < 8 || N % 8 != 0 || K < 256 || K % 256 != 0)
+    return fail(B200_EINVAL, "%s: needs N a positive multiple of 8 and K a positive multiple of 256", who);
+  if (!aligned16(scales) || !aligned16(y)) return fail(B200_EINVAL, "%s: scales and y must be 16-byte aligned", who);
+  if (!red) return fail(B200_EINVAL, "%s: null reduction descriptor", who);
+  if (red->world < 1 || red->world > 8 || red->rank < 0 || red->rank >= red->world)
+    return fail(B200_EINVAL, "%s: world %d / rank %d out of range (1..8)", who, red->world, red->rank);
+  if (red->world > 1) {
+    if (!red->epoch || !red->done_counter || !red->out || !aligned16(red->out) || red->flag_base < 0)
+      return fail(B200_EINVAL, "%s: epoch, done_counter and a 16-byte aligned out are required", who);
+    for (int r = 0; r < red->world; ++r)
+      if (!red->peer_y[r] || !aligned16(red->peer_y[r]) || !red->peer_flags[r])
+        return fail(B200_EINVAL, "%s: peer %d has a null or misaligned buffer", who, r);
+    if (red->peer_y[red->rank] != y) return fail(B200_EINVAL, "%s: y must be this rank's entry of peer_y", who);
+  }
+  rc = ensure_device();
+  if (rc) return rc;
+  rc = launch_gemv_pipe_allreduce(static_cast<const __half*>(x), static_cast<const uint32_t*>(wq),
+                                  static_cast<const __half*>(scales), static_cast<__half*>(y), M, N, K, swiglu, red,
+                                  static_cast<cudaStream_t>(stream));
+  if (rc == B200_ENOTREADY) return fail(B200_EINVAL, "%s: shape outside the fused kernel's domain", who);
+  return rc;
+}
+
 int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, const void* scales, void* y_dev,
                            void* y_host, int64_t M, int64_t N, int64_t K, void* stream) {
   if (M < 0 || N < 0 || K < 0) return fail(B200_EINVAL, "q4f16_matmul_host: negative size");

@@ -60,6 +60,20 @@ __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 // Eight fp16 at a time, fp32 inside, one round-to-nearest at the end (the same arithmetic as the
 // stand-alone RMSNorm and SwiGLU kernels).
 __device__ __forceinline__ uint4 add_f16x8(const uint4& a, const uint4& b) {
@@ -117,6 +131,23 @@ struct XLayout {
 };
 
 enum { kPrologueNone = 0, kPrologueRmsNorm = 1, kPrologueSwiGLU = 2 };
+constexpr int kMaxPeers = 8;
+constexpr uint64_t kPeerWaitNs = 2000000000ull;          // 2 s for the other GPUs to publish their partial results
+
+// Sum over tensor-parallel ranks fused into a row-parallel matmul.  y (this rank's partial result)
+// lives in memory that every peer has mapped; the CTA that finishes last on this GPU publishes a
+// flag to every peer, waits for theirs, and adds the partial results up in rank order (so every
+// rank gets the same bits) into `out`.  Peer memory is read with plain volatile loads only.
+struct PeerReduce {
+  int world = 0;                            // <= 1: off
+  int rank = 0;
+  const __half* peer_y[kMaxPeers] = {};     // rank r's partial result as mapped on this GPU (peer_y[rank] == y)
+  int* peer_flags[kMaxPeers] = {};          // rank r's flag array as mapped on this GPU
+  int flag_base = 0;                        // this reduction's `world` slots inside a flag array
+  const int* epoch = nullptr;               // device scalar: flags carry *epoch + 1 (grows from step to step)
+  int* done_counter = nullptr;              // zero between launches
+  __half* out = nullptr;                    // [M, N] fp16, local
+};
 
 struct PipeParams {
   CUtensorMap tm_w;   // uint32 {32, N, K/256}, box {32, 16, CH}, 128B swizzle
@@ -134,6 +165,7 @@ struct PipeParams {
   const __half* norm_w;      // RmsNorm: weight [K]
   __half* x_out;             // RmsNorm: fp16(x + delta) is written here by CTA 0 (or null)
   float eps;
+  PeerReduce red;
 };
 
 // Shared memory carve-up (after rounding the base up to 1024 bytes):
@@ -170,6 +202,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   float* accs = red + nred * CW * kOut;
 
   __shared__ int s_abort;                    // set once a bounded wait gives up: later waits are skipped
+  __shared__ int s_last;                     // this CTA finished last on this GPU: it adds up the ranks' partial results
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -273,10 +306,38 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         rround += (rb == 0);
       }
     }
-    return;
+    if (p.red.world > 1) {
+      // ---- this GPU's partial result is complete once every CTA has come through here ----------
+      __threadfence_system();                     // this CTA's stores to y are visible to the peers
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) last = atomicAdd(p.red.done_counter, 1) == (int)gridDim.x - 1;
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
+        const int e = *p.red.epoch + 1;
+        if (lane == 0) *p.red.done_counter = 0;
+        __threadfence_system();
+        if (lane < p.red.world) st_release_sys(p.red.peer_flags[lane] + p.red.flag_base + p.red.rank, e);
+        if (lane < p.red.world) {
+          const int* f = p.red.peer_flags[p.red.rank] + p.red.flag_base + lane;
+          const uint64_t t0 = globaltimer_ns();
+          while (ld_acquire_sys(f) < e) {
+            if (globaltimer_ns() - t0 > kPeerWaitNs) {   // a peer never published: give up, flag the error
+              atomicExch(&g_gemv_pipe_error, 16);
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+        __syncwarp();
+      }
+      if (lane == 0) *(volatile int*)&s_last = last;
+    }
+    goto tail;
   }
 
   // -------------------------------------------------------------------- consumer warps
+  {
   const int g = lane >> 2;
   const int t = lane & 3;
   constexpr int kConsumers = CW * 32;
@@ -514,6 +575,43 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
       rround += (rb == 0);
     }
   }
+  }   // (consumer scope)
+
+tail:
+  if (p.red.world > 1) {
+    // consumers wait here for the epilogue warp's verdict; in the last CTA all of them then help
+    bar_sync(3, (CW + 1) * 32);
+    if (*(volatile int*)&s_last) {
+      const int rt = warp < CW ? tid : CW * 32 + lane;         // 0 .. (CW+1)*32-1 (the TMA warp has left)
+      const int n8 = (p.M * p.N) >> 3;                         // N % 8 == 0 is checked by the caller
+      for (int i = rt; i < n8; i += (CW + 1) * 32) {
+        uint4 v[kMaxPeers];
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+          if (r < p.red.world) v[r] = ld_volatile_v4(p.red.peer_y[r] + (int64_t)i * 8);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+          if (r < p.red.world) {
+            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(h[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+        }
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        *reinterpret_cast<uint4*>(p.red.out + (int64_t)i * 8) = o;
+      }
+    }
+  }
   if (*(volatile int*)&s_abort) {
     // copies may still be in flight into this CTA's shared memory: let them land before exit
     const uint64_t t0 = globaltimer_ns();
@@ -531,7 +629,7 @@ struct Prologue {
 
 template <int NC, int CW, int CH>
 int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int M, int N, int K,
-                cudaStream_t stream, const Prologue& pro) {
+                cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   constexpr int MT = (NC + 7) / 8;
   constexpr int kOut = MT * 128;
   constexpr int KC = 256 * CH;
@@ -553,6 +651,7 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   p.x = x; p.y = y;
   p.M = M; p.N = N; p.K = K;
   p.prologue = pro.kind; p.delta = pro.delta; p.norm_w = pro.norm_w; p.x_out = pro.x_out; p.eps = pro.eps;
+  p.red = red;
   p.ntiles = (N + kRows - 1) / kRows;
   const int kpad = ((K + KC - 1) / KC) * KC;
   const int stages_per_tile = kpad / KC;
@@ -633,20 +732,36 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
 
 template <int CW, int CH>
 int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int m, int n, int k,
-                  cudaStream_t stream, const Prologue& pro) {
-  if (m == 1) return launch_pipe<1, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
-  if (m == 2) return launch_pipe<2, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
-  if (m <= 4) return launch_pipe<4, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
-  if (m <= 8) return launch_pipe<8, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
-  return launch_pipe<16, CW, CH>(x, wq, scales, y, m, n, k, stream, pro);
+                  cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
+  if (m == 1) return launch_pipe<1, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m == 2) return launch_pipe<2, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m <= 4) return launch_pipe<4, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m <= 8) return launch_pipe<8, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
+  return launch_pipe<16, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
 }
 
 int dispatch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N, int64_t K,
-                  cudaStream_t stream, const Prologue& pro) {
+                  cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   if (K % 256 != 0 || (reinterpret_cast<uintptr_t>(scales) & 15u)) return B200_ENOTREADY;
   int m = (int)M, n = (int)N, k = (int)K;
-  if (options().gemv_warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream, pro);
-  return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream, pro);
+  if (options().gemv_warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream, pro, red);
+  return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream, pro, red);
+}
+
+PeerReduce make_reduce(const B200PeerReduce* r) {
+  PeerReduce red;
+  if (!r || r->world <= 1) return red;
+  red.world = r->world;
+  red.rank = r->rank;
+  for (int i = 0; i < r->world && i < kMaxPeers; ++i) {
+    red.peer_y[i] = static_cast<const __half*>(r->peer_y[i]);
+    red.peer_flags[i] = static_cast<int*>(r->peer_flags[i]);
+  }
+  red.flag_base = r->flag_base;
+  red.epoch = static_cast<const int*>(r->epoch);
+  red.done_counter = static_cast<int*>(r->done_counter);
+  red.out = static_cast<__half*>(r->out);
+  return red;
 }
 
 }  // namespace
@@ -655,7 +770,7 @@ int dispatch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __h
 // the register-streaming kernel).
 int launch_gemv_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                      int64_t K, cudaStream_t stream) {
-  return dispatch_pipe(x, wq, scales, y, M, N, K, stream, Prologue{});
+  return dispatch_pipe(x, wq, scales, y, M, N, K, stream, Prologue{}, PeerReduce{});
 }
 
 // y = (rmsnorm(fp16(x + delta)) * norm_w) . decode(W)^T; fp16(x + delta) also goes to x_out (if given).
@@ -664,7 +779,7 @@ int launch_gemv_pipe_rmsnorm(const __half* x, const __half* delta, const __half*
                              cudaStream_t stream) {
   Prologue pro;
   pro.kind = kPrologueRmsNorm; pro.delta = delta; pro.norm_w = norm_w; pro.x_out = x_out; pro.eps = eps;
-  return dispatch_pipe(x, wq, scales, y, M, N, K, stream, pro);
+  return dispatch_pipe(x, wq, scales, y, M, N, K, stream, pro, PeerReduce{});
 }
 
 // y = (silu(gu[:, :K]) * gu[:, K:]) . decode(W)^T
@@ -672,7 +787,15 @@ int launch_gemv_pipe_swiglu(const __half* gu, const uint32_t* wq, const __half* 
                             int64_t K, cudaStream_t stream) {
   Prologue pro;
   pro.kind = kPrologueSwiGLU;
-  return dispatch_pipe(gu, wq, scales, y, M, N, K, stream, pro);
+  return dispatch_pipe(gu, wq, scales, y, M, N, K, stream, pro, PeerReduce{});
+}
+
+// Row-parallel matmul + sum over ranks in one kernel; swiglu != 0 applies the SwiGLU prologue.
+int launch_gemv_pipe_allreduce(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                               int64_t K, int swiglu, const B200PeerReduce* red, cudaStream_t stream) {
+  Prologue pro;
+  pro.kind = swiglu ? kPrologueSwiGLU : kPrologueNone;
+  return dispatch_pipe(x, wq, scales, y, M, N, K, stream, pro, make_reduce(red));
 }
 
 int gemv_pipe_error_read_and_clear() {

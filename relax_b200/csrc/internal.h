@@ -37,6 +37,8 @@ int launch_gemv_pipe_rmsnorm(const __half* x, const __half* delta, const __half*
                              cudaStream_t stream);
 int launch_gemv_pipe_swiglu(const __half* gu, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                             int64_t K, cudaStream_t stream);
+int launch_gemv_pipe_allreduce(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                               int64_t K, int swiglu, const B200PeerReduce* red, cudaStream_t stream);
 int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
 

@@ -15,8 +15,8 @@ Layout per rank (world size t, hidden H, heads nh, head dim 128, intermediate I)
 """
 from __future__ import annotations
 
+import ctypes
 import dataclasses
-import math
 
 import numpy as np
 import torch
@@ -101,7 +101,7 @@ class DecodeEngine:
     """
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
-                 device, rank: int = 0, world: int = 1, group=None, fused: bool = True):
+                 device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
@@ -139,6 +139,46 @@ class DecodeEngine:
         self.gathered = torch.zeros((world, B, vl), **f16) if vl and world > 1 else None
         self.graph = None
         self.launches_per_step = 0
+        # tensor parallel: the sum over ranks after o and down runs inside those matmul kernels over
+        # NVLink peer memory (b200_q4f16_gemv_allreduce) when the batch is in the skinny kernel's range;
+        # otherwise (or with peer_reduce=False) it is an NCCL all-reduce
+        self.peer = None
+        self.epoch = torch.zeros((1,), dtype=torch.int32, device=self.device)
+        if world > 1 and peer_reduce and B <= 16:
+            self._setup_peer_reduce()
+
+    def _setup_peer_reduce(self):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        B, H, nl, world = self.batch, self.cfg.hidden, len(self.layers), self.world
+        ybytes = B * H * 2
+        ybytes = (ybytes + 255) // 256 * 256
+        fbytes = 2 * nl * world * 4
+        total = 2 * ybytes + fbytes
+        buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        buf.zero_()
+        torch.cuda.synchronize(self.device)
+        hdl = symm_mem.rendezvous(buf, group=self.group if self.group is not None else torch.distributed.group.WORLD)
+        torch.distributed.barrier(group=self.group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self.peer = {
+            "buf": buf, "hdl": hdl,
+            "y": [[p + k * ybytes for p in ptrs] for k in range(2)],          # [kind][rank]
+            "flags": [p + 2 * ybytes for p in ptrs],
+            "done": torch.zeros((1,), dtype=torch.int32, device=self.device),
+        }
+
+    def _reduce_desc(self, kind: int, layer: int, out):
+        d = _lib.PeerReduce()
+        d.world, d.rank = self.world, self.rank
+        for r in range(self.world):
+            d.peer_y[r] = self.peer["y"][kind][r]
+            d.peer_flags[r] = self.peer["flags"][r]
+        d.flag_base = (kind * len(self.layers) + layer) * self.world
+        d.epoch = self.epoch.data_ptr()
+        d.done_counter = self.peer["done"].data_ptr()
+        d.out = out.data_ptr()
+        return d
 
     # ------------------------------------------------------------------ kernel calls
     def _check(self, rc):
@@ -171,12 +211,22 @@ class DecodeEngine:
                                           self.max_ctx, sp))
         self._check(L.b200_attn_decode(self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.pos.data_ptr(),
                                        self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
-        self._matmul(self.attn, w["o"], self.o, H, hl, sp)
-        self._allreduce(self.o)
+        if self.peer is not None:
+            d = self._reduce_desc(0, i, self.o)
+            self._check(L.b200_q4f16_gemv_allreduce(self.attn.data_ptr(), w["o"][0].data_ptr(), w["o"][1].data_ptr(),
+                                                    self.peer["y"][0][self.rank], B, H, hl, 0, ctypes.byref(d), sp))
+        else:
+            self._matmul(self.attn, w["o"], self.o, H, hl, sp)
+            self._allreduce(self.o)
         if self.fused:
             self._check(L.b200_q4f16_gemv_rmsnorm(self.x2.data_ptr(), self.o.data_ptr(), w["norm2"].data_ptr(), self.x.data_ptr(),
                                                   cfg.eps, w["gu"][0].data_ptr(), w["gu"][1].data_ptr(), self.gu.data_ptr(),
                                                   B, 2 * il, H, sp))
+            if self.peer is not None:
+                d = self._reduce_desc(1, i, self.down)
+                self._check(L.b200_q4f16_gemv_allreduce(self.gu.data_ptr(), w["down"][0].data_ptr(), w["down"][1].data_ptr(),
+                                                        self.peer["y"][1][self.rank], B, H, il, 1, ctypes.byref(d), sp))
+                return self.down
             self._check(L.b200_q4f16_gemv_swiglu(self.gu.data_ptr(), w["down"][0].data_ptr(), w["down"][1].data_ptr(),
                                                  self.down.data_ptr(), B, H, il, sp))
         else:
@@ -184,6 +234,11 @@ class DecodeEngine:
                                        cfg.eps, sp))
             self._matmul(self.h, w["gu"], self.gu, 2 * il, H, sp)
             self._check(L.b200_silu_mul(self.gu.data_ptr(), self.act.data_ptr(), B, il, sp))
+            if self.peer is not None:
+                d = self._reduce_desc(1, i, self.down)
+                self._check(L.b200_q4f16_gemv_allreduce(self.act.data_ptr(), w["down"][0].data_ptr(), w["down"][1].data_ptr(),
+                                                        self.peer["y"][1][self.rank], B, H, il, 0, ctypes.byref(d), sp))
+                return self.down
             self._matmul(self.act, w["down"], self.down, H, il, sp)
         self._allreduce(self.down)
         return self.down
@@ -209,10 +264,11 @@ class DecodeEngine:
                 self.logits.view(B, self.world, -1).copy_(self.gathered.permute(1, 0, 2))
             self.tokens.copy_(torch.argmax(self.logits, dim=1).to(torch.int32))
         self._check(L.b200_advance_pos(self.pos.data_ptr(), 1, sp))
+        self._check(L.b200_advance_pos(self.epoch.data_ptr(), 1, sp))
 
     def kernels_per_step(self) -> int:
         """Kernels of this library launched by one step (embed + 7 or 11 per layer + final norm + advance)."""
-        return 1 + len(self.layers) * (7 if self.fused else 11) + 1 + 1
+        return 1 + len(self.layers) * (7 if self.fused else 11) + 1 + 2
 
     def capture(self, stream):
         """Captures one step into a CUDA graph on `stream` (after one eager warm-up step, which
