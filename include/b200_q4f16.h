@@ -205,6 +205,16 @@ B200_API int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t m
 B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
                               void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);
 
+/* Rotary embedding of q and k, KV append at *pos, attention over positions 0..*pos and the merge of
+ * the per-chunk partials in one launch (what b200_rope_kv_append + b200_attn_decode do in three).
+ * qkv fp16 [B, 3*nh*128] = [q | k | v] of the new token; out fp16 [B, nh*128].  `scratch`:
+ * b200_attn_decode_fused_scratch_bytes(B, nh, max_ctx) bytes of caller-owned device memory whose last
+ * B*nh int32 (the arrival counters) must be ZERO before the first call; the kernel leaves them zero. */
+B200_API int64_t b200_attn_decode_fused_scratch_bytes(int64_t B, int64_t nh, int64_t max_ctx);
+B200_API int b200_attn_decode_fused(const void* qkv, const void* cos_t, const void* sin_t, const void* pos, void* k_cache,
+                                    void* v_cache, void* out, void* scratch, int64_t B, int64_t nh, int64_t max_ctx,
+                                    void* cuda_stream);
+
 /* Same attention for callers that cannot hand over scratch memory.  (No counterpart in the
  * reference.)  Some hosts of this library are not allowed to allocate device memory at the point
  * where they call it: a runtime whose memory planner has already fixed every buffer of the step,

@@ -79,6 +79,8 @@ PROTOTYPES = {
     "b200_rope_kv_append": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_scratch_bytes": (_i64, [_i64, _i64, _i64]),
     "b200_attn_decode": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_attn_decode_fused_scratch_bytes": (_i64, [_i64, _i64, _i64]),
+    "b200_attn_decode_fused": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_static": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_silu_mul": (_ci, [_vp, _vp, _i64, _i64, _vp]),
     "b200_embed_rows": (_ci, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),

@@ -211,6 +211,176 @@ attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restric
   if (d == 0) { out[0] = M; out[1] = L; }
 }
 
+// Rotary embedding + KV append + attention + merge of the partials in ONE launch.
+// grid (nsplit, nh, B), 128 threads.  CTA (split, h, b):
+//   * rotates q of head h itself (lane owns dims 4*lane..+3; its rotate-half partner is lane ^ 16);
+//   * if its chunk holds the new token, rotates k, writes k and v into the caches at *pos first;
+//   * runs the online softmax over its chunk as attn_decode_partial_kernel does;
+//   * bumps a per-(b, h) counter; the CTA that arrives last merges all chunks' partials and stores
+//     fp16.  The counters live after the partials in `scratch`, must be zero before the first call
+//     and are left zero.
+__global__ void __launch_bounds__(128)
+attn_decode_fused_kernel(const __half* __restrict__ qkv, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                         const int* __restrict__ pos_ptr, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
+                         __half* __restrict__ out, float* __restrict__ scratch, int nh, int max_ctx, int nsplit,
+                         float scale_log2e) {
+  ptx::pdl_wait();
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int pos = pos_ptr[0];
+  const int ctx = pos + 1;
+  const int used = (ctx + kAttnChunk - 1) / kAttnChunk;
+  if (split >= used) return;
+  const int t0 = split * kAttnChunk;
+  const int t1 = min(ctx, t0 + kAttnChunk);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* part = scratch + (((int64_t)b * nh + h) * nsplit + split) * 130;
+  int* counters = reinterpret_cast<int*>(scratch + (int64_t)gridDim.z * nh * nsplit * 130);
+  __shared__ float sm_m[4], sm_l[4], sm_acc[4][128];
+  __shared__ int s_last;
+
+  const __half* row = qkv + (int64_t)b * 3 * nh * 128;
+  const int d0 = lane * 4;                         // this lane's dims
+  const int r0 = d0 & 63;                          // their rotation index (pairs i <-> i + 64)
+  const float4 cs = *reinterpret_cast<const float4*>(cos_t + (int64_t)pos * 64 + r0);
+  const float4 sn = *reinterpret_cast<const float4*>(sin_t + (int64_t)pos * 64 + r0);
+  const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s[4] = {sn.x, sn.y, sn.z, sn.w};
+  const float sign = lane < 16 ? -1.f : 1.f;       // first half: a*c - b*s, second half: b*c + a*s
+  auto rotate = [&](const __half* v, float (&o)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(v + d0);
+    const __half2* hh = reinterpret_cast<const __half2*>(&raw);
+    const float2 a = __half22float2(hh[0]), e = __half22float2(hh[1]);
+    const float mine[4] = {a.x, a.y, e.x, e.y};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, mine[j], 16);
+      // round to fp16 as the stand-alone rotary kernel does (q and k are fp16 tensors in the layer)
+      o[j] = __half2float(__float2half_rn(mine[j] * c[j] + sign * other * s[j]));
+    }
+  };
+
+  if (split == used - 1 && warp == 0) {
+    // the new token belongs to this chunk: put its rotated k and its v into the caches first
+    float kr[4];
+    rotate(row + (nh + h) * 128, kr);
+    const int64_t slot = (((int64_t)b * max_ctx + pos) * nh + h) * 128 + d0;
+    uint2 kw;
+    __half2* kh2 = reinterpret_cast<__half2*>(&kw);
+    kh2[0] = __floats2half2_rn(kr[0], kr[1]);
+    kh2[1] = __floats2half2_rn(kr[2], kr[3]);
+    *reinterpret_cast<uint2*>(k_cache + slot) = kw;
+    *reinterpret_cast<uint2*>(v_cache + slot) = *reinterpret_cast<const uint2*>(row + (2 * nh + h) * 128 + d0);
+  }
+  float qf[4];
+  rotate(row + h * 128, qf);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) qf[j] *= scale_log2e;
+  __syncthreads();                                 // the appended token is visible to the whole CTA
+
+  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int64_t tok_stride = (int64_t)nh * 128;
+  const __half* kb = k_cache + ((int64_t)b * max_ctx * nh + h) * 128 + d0;
+  const __half* vb = v_cache + ((int64_t)b * max_ctx * nh + h) * 128 + d0;
+  constexpr int kTok = 8;
+  for (int tb = t0 + warp * kTok; tb < t1; tb += 4 * kTok) {
+    uint2 kv[kTok], vv[kTok];
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      const int t = min(tb + j, t1 - 1);
+      kv[j] = *reinterpret_cast<const uint2*>(kb + t * tok_stride);
+      vv[j] = *reinterpret_cast<const uint2*>(vb + t * tok_stride);
+    }
+    float sc[kTok];
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      const __half2* kh = reinterpret_cast<const __half2*>(&kv[j]);
+      const float2 k01 = __half22float2(kh[0]), k23 = __half22float2(kh[1]);
+      sc[j] = qf[0] * k01.x + qf[1] * k01.y + qf[2] * k23.x + qf[3] * k23.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int j = 0; j < kTok; ++j) sc[j] += __shfl_xor_sync(0xffffffffu, sc[j], o);
+    float mn = m;
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      if (tb + j >= t1) sc[j] = -INFINITY;
+      mn = fmaxf(mn, sc[j]);
+    }
+    const float corr = exp2f(m - mn);
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      const float pj = exp2f(sc[j] - mn);
+      const __half2* vh = reinterpret_cast<const __half2*>(&vv[j]);
+      const float2 v01 = __half22float2(vh[0]), v23 = __half22float2(vh[1]);
+      l += pj;
+      acc[0] += pj * v01.x;
+      acc[1] += pj * v01.y;
+      acc[2] += pj * v23.x;
+      acc[3] += pj * v23.y;
+    }
+    m = mn;
+  }
+  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) sm_acc[warp][lane * 4 + j] = acc[j];
+  __syncthreads();
+  ptx::pdl_launch_dependents();
+  const int d = threadIdx.x;
+  {
+    const float M = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = (sm_m[w] == -INFINITY) ? 0.f : exp2f(sm_m[w] - M);
+      L += sm_l[w] * f;
+      A += sm_acc[w][d] * f;
+    }
+    part[2 + d] = A;
+    if (d == 0) { part[0] = M; part[1] = L; }
+  }
+  // ---- the CTA that arrives last for this (b, h) merges the chunks ---------------------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&counters[b * nh + h], 1) == used - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x == 0) counters[b * nh + h] = 0;
+  const float* p = scratch + ((int64_t)b * nh + h) * nsplit * 130;
+  // sixteen chunks per round, all loads of a round issued together (the partials sit in L2)
+  float M = -INFINITY, L = 0.f, A = 0.f;
+  for (int s0 = 0; s0 < used; s0 += 16) {
+    float Ms[16], Ls[16], As[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int si = min(s0 + j, used - 1);
+      Ms[j] = __ldcg(p + si * 130);
+      Ls[j] = __ldcg(p + si * 130 + 1);
+      As[j] = __ldcg(p + si * 130 + 2 + d);
+    }
+    float Mn = M;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (s0 + j < used) Mn = fmaxf(Mn, Ms[j]);
+    const float corr = exp2f(M - Mn);            // first round: exp2f(-inf) = 0
+    L *= corr;
+    A *= corr;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (s0 + j < used) {
+        const float f = exp2f(Ms[j] - Mn);
+        L += Ls[j] * f;
+        A += As[j] * f;
+      }
+    }
+    M = Mn;
+  }
+  out[((int64_t)b * nh + h) * 128 + d] = __float2half_rn(A / L);
+}
+
 // Merges the nsplit partials of one (batch, head) and writes fp16 [B, nh*128].  grid (nh, B), 128 threads.
 __global__ void __launch_bounds__(128)
 attn_decode_combine_kernel(const float* __restrict__ scratch, const int* __restrict__ pos_ptr, __half* __restrict__ out,
@@ -333,6 +503,25 @@ int b200_rope_kv_append(const void* qkv, const void* cos_t, const void* sin_t, c
 int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t max_ctx) {
   int64_t nsplit = (max_ctx + kAttnChunk - 1) / kAttnChunk;
   return B * nh * nsplit * 130 * (int64_t)sizeof(float);
+}
+
+int64_t b200_attn_decode_fused_scratch_bytes(int64_t B, int64_t nh, int64_t max_ctx) {
+  return b200_attn_decode_scratch_bytes(B, nh, max_ctx) + B * nh * (int64_t)sizeof(int);
+}
+
+int b200_attn_decode_fused(const void* qkv, const void* cos_t, const void* sin_t, const void* pos, void* k_cache, void* v_cache,
+                           void* out, void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* stream) {
+  if (B <= 0 || nh <= 0 || max_ctx <= 0 || B > 65535 || nh > 65535) return fail(B200_EINVAL, "attn_decode_fused: bad sizes");
+  if (!qkv || !cos_t || !sin_t || !pos || !k_cache || !v_cache || !out || !scratch)
+    return fail(B200_EINVAL, "attn_decode_fused: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  const int nsplit = (int)((max_ctx + kAttnChunk - 1) / kAttnChunk);
+  const float scale_log2e = 1.4426950408889634f / sqrtf(128.f);
+  return launch("attn_decode_fused", attn_decode_fused_kernel, dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B), dim3(128), 0,
+                static_cast<cudaStream_t>(stream), (const __half*)qkv, (const float*)cos_t, (const float*)sin_t,
+                (const int*)pos, (__half*)k_cache, (__half*)v_cache, (__half*)out, (float*)scratch, (int)nh, (int)max_ctx,
+                nsplit, scale_log2e);
 }
 
 int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out, void* scratch,

@@ -136,8 +136,9 @@ constexpr uint64_t kPeerWaitNs = 2000000000ull;          // 2 s for the other GP
 
 // Sum over tensor-parallel ranks fused into a row-parallel matmul.  y (this rank's partial result)
 // lives in memory that every peer has mapped; the CTA that finishes last on this GPU publishes a
-// flag to every peer, waits for theirs, and adds the partial results up in rank order (so every
-// rank gets the same bits) into `out`.  Peer memory is read with plain volatile loads only.
+// flag to every rank; every CTA then waits for all ranks' flags and adds up its slice of the
+// partial results in rank order (so every rank gets the same bits) into `out`.  Peer memory is
+// read with plain volatile loads only.
 struct PeerReduce {
   int world = 0;                            // <= 1: off
   int rank = 0;
@@ -202,7 +203,6 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   float* accs = red + nred * CW * kOut;
 
   __shared__ int s_abort;                    // set once a bounded wait gives up: later waits are skipped
-  __shared__ int s_last;                     // this CTA finished last on this GPU: it adds up the ranks' partial results
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -308,30 +308,31 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     }
     if (p.red.world > 1) {
       // ---- this GPU's partial result is complete once every CTA has come through here ----------
-      __threadfence_system();                     // this CTA's stores to y are visible to the peers
+      __threadfence();                            // this CTA's stores to y are in L2, where the peers read them
       __syncwarp();
+      const int e = *p.red.epoch + 1;
       int last = 0;
       if (lane == 0) last = atomicAdd(p.red.done_counter, 1) == (int)gridDim.x - 1;
       last = __shfl_sync(0xffffffffu, last, 0);
       if (last) {
-        const int e = *p.red.epoch + 1;
         if (lane == 0) *p.red.done_counter = 0;
         __threadfence_system();
+        // tell every rank (this one included) that rank `rank`'s partial result is complete
         if (lane < p.red.world) st_release_sys(p.red.peer_flags[lane] + p.red.flag_base + p.red.rank, e);
-        if (lane < p.red.world) {
-          const int* f = p.red.peer_flags[p.red.rank] + p.red.flag_base + lane;
-          const uint64_t t0 = globaltimer_ns();
-          while (ld_acquire_sys(f) < e) {
-            if (globaltimer_ns() - t0 > kPeerWaitNs) {   // a peer never published: give up, flag the error
-              atomicExch(&g_gemv_pipe_error, 16);
-              break;
-            }
-            __nanosleep(64);
+      }
+      // every CTA waits for every rank's flag (all CTAs of the grid are resident, none of them is
+      // waiting for an SM), then adds up its own slice of the result
+      if (lane < p.red.world) {
+        const int* f = p.red.peer_flags[p.red.rank] + p.red.flag_base + lane;
+        const uint64_t t0 = globaltimer_ns();
+        while (ld_acquire_sys(f) < e) {
+          if (globaltimer_ns() - t0 > kPeerWaitNs) {   // a rank never published: give up, flag the error
+            atomicExch(&g_gemv_pipe_error, 16);
+            break;
           }
         }
-        __syncwarp();
       }
-      if (lane == 0) *(volatile int*)&s_last = last;
+      __syncwarp();
     }
     goto tail;
   }
@@ -579,37 +580,36 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
 
 tail:
   if (p.red.world > 1) {
-    // consumers wait here for the epilogue warp's verdict; in the last CTA all of them then help
+    // the consumers wait here until the epilogue warp has seen every rank's flag; then the CTA adds
+    // up items blockIdx.x, blockIdx.x + gridDim.x, ... (8 outputs each), all peers' loads in flight at once
     bar_sync(3, (CW + 1) * 32);
-    if (*(volatile int*)&s_last) {
-      const int rt = warp < CW ? tid : CW * 32 + lane;         // 0 .. (CW+1)*32-1 (the TMA warp has left)
-      const int n8 = (p.M * p.N) >> 3;                         // N % 8 == 0 is checked by the caller
-      for (int i = rt; i < n8; i += (CW + 1) * 32) {
-        uint4 v[kMaxPeers];
+    const int rt = warp < CW ? tid : CW * 32 + lane;           // 0 .. (CW+1)*32-1 (the TMA warp has left)
+    const int n8 = (p.M * p.N) >> 3;                           // N % 8 == 0 is checked by the caller
+    for (int i = blockIdx.x + rt * gridDim.x; i < n8; i += (CW + 1) * 32 * gridDim.x) {
+      uint4 v[kMaxPeers];
 #pragma unroll
-        for (int r = 0; r < kMaxPeers; ++r)
-          if (r < p.red.world) v[r] = ld_volatile_v4(p.red.peer_y[r] + (int64_t)i * 8);
-        float acc[8];
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < p.red.world) v[r] = ld_volatile_v4(p.red.peer_y[r] + (int64_t)i * 8);
+      float acc[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-        for (int r = 0; r < kMaxPeers; ++r) {
-          if (r < p.red.world) {
-            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < p.red.world) {
+          const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __half22float2(h[j]);
-              acc[2 * j] += f.x;
-              acc[2 * j + 1] += f.y;
-            }
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
           }
         }
-        uint4 o;
-        __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
-        *reinterpret_cast<uint4*>(p.red.out + (int64_t)i * 8) = o;
       }
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+      *reinterpret_cast<uint4*>(p.red.out + (int64_t)i * 8) = o;
     }
   }
   if (*(volatile int*)&s_abort) {

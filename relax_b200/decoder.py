@@ -101,7 +101,8 @@ class DecodeEngine:
     """
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
-                 device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True):
+                 device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True,
+                 fused_attention: bool = True):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
@@ -116,6 +117,7 @@ class DecodeEngine:
         # fused: RMSNorm (+ residual add) and SwiGLU run inside the staging of the next skinny matmul
         # (7 kernels per layer instead of 11); needs batch <= 16, the skinny kernel's range
         self.fused = bool(fused) and B <= 16
+        self.fused_attention = bool(fused_attention)
         self.x = torch.zeros((B, H), **f16)            # residual stream
         self.x2 = torch.zeros((B, H), **f16)           # its second buffer (fused path ping-pongs)
         self.h = torch.zeros((B, H), **f16)            # normalised activations
@@ -128,8 +130,8 @@ class DecodeEngine:
         self.down = torch.zeros((B, H), **f16)
         self.kc = [torch.zeros((B, max_ctx, self.nh_local, 128), **f16) for _ in layers]
         self.vc = [torch.zeros((B, max_ctx, self.nh_local, 128), **f16) for _ in layers]
-        nbytes = int(self.L.b200_attn_decode_scratch_bytes(B, self.nh_local, max_ctx))
-        self.scratch = torch.empty((max(nbytes, 4) // 4,), dtype=torch.float32, device=self.device)
+        nbytes = int(self.L.b200_attn_decode_fused_scratch_bytes(B, self.nh_local, max_ctx))
+        self.scratch = torch.zeros((max(nbytes, 4) // 4,), dtype=torch.float32, device=self.device)   # counters start at 0
         self.pos = torch.zeros((1,), dtype=torch.int32, device=self.device)
         self.tokens = torch.zeros((B,), dtype=torch.int32, device=self.device)
         self.cos, self.sin = rope_tables(max_ctx, 128, cfg.theta, self.device)
@@ -206,11 +208,17 @@ class DecodeEngine:
         else:
             self._check(L.b200_rmsnorm(self.x.data_ptr(), dptr, w["norm1"].data_ptr(), self.h.data_ptr(), B, H, cfg.eps, sp))
             self._matmul(self.h, w["qkv"], self.qkv, 3 * hl, H, sp)
-        self._check(L.b200_rope_kv_append(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
-                                          self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), B, self.nh_local,
-                                          self.max_ctx, sp))
-        self._check(L.b200_attn_decode(self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.pos.data_ptr(),
-                                       self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
+        if self.fused_attention:
+            # rotary embedding + KV append + attention + merge in one launch
+            self._check(L.b200_attn_decode_fused(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
+                                                 self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.attn.data_ptr(),
+                                                 self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
+        else:
+            self._check(L.b200_rope_kv_append(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
+                                              self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), B, self.nh_local,
+                                              self.max_ctx, sp))
+            self._check(L.b200_attn_decode(self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.pos.data_ptr(),
+                                           self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
         if self.peer is not None:
             d = self._reduce_desc(0, i, self.o)
             self._check(L.b200_q4f16_gemv_allreduce(self.attn.data_ptr(), w["o"][0].data_ptr(), w["o"][1].data_ptr(),
@@ -267,8 +275,8 @@ class DecodeEngine:
         self._check(L.b200_advance_pos(self.epoch.data_ptr(), 1, sp))
 
     def kernels_per_step(self) -> int:
-        """Kernels of this library launched by one step (embed + 7 or 11 per layer + final norm + advance)."""
-        return 1 + len(self.layers) * (7 if self.fused else 11) + 1 + 2
+        """Kernels of this library launched by one step (embed + 5 or 11 per layer + final norm + advance)."""
+        return 1 + len(self.layers) * ((5 if self.fused else 9) + (0 if self.fused_attention else 2)) + 1 + 2
 
     def capture(self, stream):
         """Captures one step into a CUDA graph on `stream` (after one eager warm-up step, which

@@ -97,6 +97,23 @@ def test_rope_append_attention(cuda_lib, B, nh, ctx, max_ctx):
     torch.cuda.synchronize()
     ref = odec.attention_decode(q_out.cpu().numpy(), tk.cpu().numpy(), tv.cpu().numpy(), ctx)
     close(out.cpu().numpy(), ref, 4e-3, 2e-3, "attention")
+    # the one-launch form (rotary + append + attention + merge) on fresh copies of the caches, twice in a
+    # row through the same scratch (the arrival counters must come back to zero)
+    kc0 = kc.copy(); kc0[:, pos] = 0
+    vc0 = vc.copy(); vc0[:, pos] = 0
+    fbytes = cuda_lib.b200_attn_decode_fused_scratch_bytes(B, nh, max_ctx)
+    fscratch = torch.zeros(fbytes // 4, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        tk2, tv2 = dev(kc0), dev(vc0)
+        out2 = torch.empty((B, nh * D), dtype=torch.float16, device="cuda")
+        assert cuda_lib.b200_attn_decode_fused(tq.data_ptr(), tcos.data_ptr(), tsin.data_ptr(), tpos.data_ptr(), tk2.data_ptr(),
+                                               tv2.data_ptr(), out2.data_ptr(), fscratch.data_ptr(), B, nh, max_ctx, 0) == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        close(tk2.cpu().numpy()[:, pos], k, 2e-3, 2e-3, "rotated k appended by the fused kernel")
+        assert (tk2.cpu().numpy()[:, :pos].view(np.uint16) == kc[:, :pos].view(np.uint16)).all(), "older cache entries untouched"
+        assert (tv2.cpu().numpy().view(np.uint16) == tv.cpu().numpy().view(np.uint16)).all()
+        close(out2.cpu().numpy(), ref, 4e-3, 2e-3, "fused attention")
+    assert int(fscratch[-B * nh:].view(torch.int32).abs().sum().item()) == 0, "arrival counters are left at zero"
 
 
 def test_embed_and_advance(cuda_lib):
