@@ -102,7 +102,7 @@ class DecodeEngine:
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
                  device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True,
-                 fused_attention: bool = True):
+                 fused_attention: bool = False):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
