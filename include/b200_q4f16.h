@@ -104,6 +104,12 @@ B200_API int b200_q4f16_gemv(const void* x, const void* wq, const void* scales, 
                     int64_t K, void* cuda_stream);
 B200_API int b200_q4f16_gemm(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
                     int64_t K, void* cuda_stream);
+/* Weight-stationary tensor-core kernel for mid-sized batches (1 <= M <= 128, K % 256 == 0, scales
+ * 16-byte aligned): 128 weight rows are the MMA's M, the batch its N, K is split over a thread-block
+ * cluster whose partial tiles are added through distributed shared memory.  b200_q4f16_matmul picks
+ * it for 16 < M <= 128. */
+B200_API int b200_q4f16_gemm_ws(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
+                                int64_t K, void* cuda_stream);
 
 /* Same matmul with the activation and the result in HOST memory (pinned memory makes the
  * copies asynchronous): copies x to `x_dev`, runs the kernel, copies `y_dev` back to y_host,

@@ -67,6 +67,7 @@ PROTOTYPES = {
     "b200_q4f16_matmul": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_gemv": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_gemm": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_gemm_ws": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_matmul_host": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_matmul_dl": (_ci, [_dlp, _dlp, _dlp, _dlp]),
     "b200_q4f16_dequantize_dl": (_ci, [_dlp, _dlp, _dlp]),

@@ -95,7 +95,7 @@ int zero_output(void* y, int64_t M, int64_t N, cudaStream_t s) {
   return B200_OK;
 }
 
-enum Family { kAuto, kGemv, kGemm };
+enum Family { kAuto, kGemv, kGemm, kGemmWs };
 
 int matmul_impl(Family fam, const char* who, const void* x, const void* wq, const void* scales, void* y, int64_t M,
                 int64_t N, int64_t K, void* stream) {
@@ -114,6 +114,12 @@ int matmul_impl(Family fam, const char* who, const void* x, const void* wq, cons
   auto sh = static_cast<const __half*>(scales);
   auto yh = static_cast<__half*>(y);
   if (use_gemv) return launch_gemv(xh, wh, sh, yh, M, N, K, s);
+  if (fam == kGemmWs || (fam == kAuto && M <= options().gemm_ws_max_m)) {
+    // mid-sized batches: weights stream once through the weight-stationary kernel
+    rc = launch_gemm_ws(xh, wh, sh, yh, M, N, K, s);
+    if (rc != B200_ENOTREADY) return rc;
+    if (fam == kGemmWs) return fail(B200_EINVAL, "%s: the weight-stationary kernel takes 1 <= M <= 128, K %% 256 == 0, 16-byte aligned scales", who);
+  }
   return launch_gemm(xh, wh, sh, yh, M, N, K, s);
 }
 
@@ -193,6 +199,8 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "gemv.ctas_per_sm")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemv.ctas_per_sm in 0..8"); o.gemv_ctas_per_sm = v; }
   else if (!strcmp(name, "gemm.variant")) { if (v < 0 || v > 63) return fail(B200_EINVAL, "gemm.variant in 0..63"); o.gemm_variant = v; }
   else if (!strcmp(name, "gemm.stages")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemm.stages in 0..8"); o.gemm_stages = v; }
+  else if (!strcmp(name, "gemm.ws_ksplit")) { if (v < 0 || v > 8 || (v & (v - 1))) return fail(B200_EINVAL, "gemm.ws_ksplit is 0, 1, 2, 4 or 8"); o.gemm_ws_ksplit = v; }
+  else if (!strcmp(name, "gemm.ws_max_m")) { if (v < 0 || v > 128) return fail(B200_EINVAL, "gemm.ws_max_m in 0..128"); o.gemm_ws_max_m = v; }
   else if (!strcmp(name, "gemm.max_ctas")) { if (v < 0 || v > 1024) return fail(B200_EINVAL, "gemm.max_ctas in 0..1024"); o.gemm_max_ctas = v; }
   else return fail(B200_EINVAL, "set_option: unknown option '%s'", name);
   return B200_OK;
@@ -209,6 +217,8 @@ int64_t b200_get_option(const char* name) {
   if (!strcmp(name, "gemm.variant")) return o.gemm_variant;
   if (!strcmp(name, "gemm.stages")) return o.gemm_stages;
   if (!strcmp(name, "gemm.max_ctas")) return o.gemm_max_ctas;
+  if (!strcmp(name, "gemm.ws_ksplit")) return o.gemm_ws_ksplit;
+  if (!strcmp(name, "gemm.ws_max_m")) return o.gemm_ws_max_m;
   return -1;
 }
 
@@ -300,6 +310,11 @@ int b200_q4f16_gemv_allreduce(const void* x, const void* wq, const void* scales,
                                   static_cast<cudaStream_t>(stream));
   if (rc == B200_ENOTREADY) return fail(B200_EINVAL, "%s: shape outside the fused kernel's domain", who);
   return rc;
+}
+
+int b200_q4f16_gemm_ws(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                       void* stream) {
+  return matmul_impl(kGemmWs, "q4f16_gemm_ws", x, wq, scales, y, M, N, K, stream);
 }
 
 int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, const void* scales, void* y_dev,

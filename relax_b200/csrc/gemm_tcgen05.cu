@@ -440,6 +440,8 @@ int gemm_error_read_and_clear() {
   return v & 0xff;
 }
 
-int device_error_flags_read_and_clear() { return gemv_pipe_error_read_and_clear() | (gemm_error_read_and_clear() << 8); }
+int device_error_flags_read_and_clear() {
+  return gemv_pipe_error_read_and_clear() | (gemm_error_read_and_clear() << 8) | (gemm_ws_error_read_and_clear() << 16);
+}
 
 }  // namespace b200

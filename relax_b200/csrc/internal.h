@@ -22,6 +22,8 @@ struct Options {
   int64_t gemm_variant = 0;   // 0 = auto
   int64_t gemm_stages = 0;
   int64_t gemm_max_ctas = 0;  // 0 = one per SM; smaller values force several tiles per CTA (tests)
+  int64_t gemm_ws_ksplit = 0; // 0 = auto: K slices (= cluster size) of the weight-stationary kernel
+  int64_t gemm_ws_max_m = 128; // largest M the automatic dispatch gives to the weight-stationary kernel (0 = never)
 };
 Options& options();
 
@@ -39,13 +41,16 @@ int launch_gemv_pipe_swiglu(const __half* gu, const uint32_t* wq, const __half* 
                             int64_t K, cudaStream_t stream);
 int launch_gemv_pipe_allreduce(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                                int64_t K, int swiglu, const B200PeerReduce* red, cudaStream_t stream);
+int launch_gemm_ws(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
+                   int64_t K, cudaStream_t stream);
 int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
 
-// Reads and clears the per-kernel device error words (bit 0-7: skinny pipeline, 8-15: tensor-core GEMM).
+// Reads and clears the per-kernel device error words (bit 0-7: skinny pipeline, 8-15: tensor-core GEMM, 16-23: weight-stationary GEMM).
 int device_error_flags_read_and_clear();
 int gemv_pipe_error_read_and_clear();
 int gemm_error_read_and_clear();
+int gemm_ws_error_read_and_clear();
 
 // Device capability check, cached per device; 0 when the current device is sm_100.
 int ensure_device();

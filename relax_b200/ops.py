@@ -79,7 +79,8 @@ def q4f16_matmul(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, out: t
             vx, vw, vs, vy = (_DLView(t) for t in (x, wq, scales, out))
             _lib.check(L.b200_q4f16_matmul_dl(vx.ptr(), vw.ptr(), vs.ptr(), vy.ptr()))
         return out
-    fn = {"gemv": L.b200_q4f16_gemv, "gemm": L.b200_q4f16_gemm, "matmul": L.b200_q4f16_matmul}[family]
+    fn = {"gemv": L.b200_q4f16_gemv, "gemm": L.b200_q4f16_gemm, "gemm_ws": L.b200_q4f16_gemm_ws,
+          "matmul": L.b200_q4f16_matmul}[family]
     M, K = x.shape
     N = wq.shape[0]
     with _on(x.device):

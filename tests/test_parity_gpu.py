@@ -318,3 +318,51 @@ def test_gemm_many_tiles_per_cta_bit_exact(cuda_lib, k, tiles, ctas):
     finally:
         relax_b200.set_option("gemm.max_ctas", 0)
     assert cuda_lib.b200_device_error_flags() == 0
+
+
+# ------------------------------------------------------------------------------ weight-stationary GEMM (mid-sized batches)
+@pytest.mark.parametrize("ksplit", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (9, 300, 1024), (16, 4096, 4096), (17, 129, 2048), (33, 1000, 4096),
+                                   (64, 4096, 4096), (100, 512, 11008), (128, 2000, 2048), (128, 4096, 11008)])
+def test_gemm_ws_shapes(cuda_lib, m, n, k, ksplit):
+    x, wq, s = synth.make_case(m, n, k, seed=m + n + k)
+    try:
+        relax_b200.set_option("gemm.ws_ksplit", ksplit)
+        out = run_matmul(x, wq, s, family="gemm_ws")
+    finally:
+        relax_b200.set_option("gemm.ws_ksplit", 0)
+    assert_matmul_close(out, x, wq, s, f"gemm_ws M={m} N={n} K={k} ksplit={ksplit}")
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+def test_gemm_ws_one_hot_selects_weights_exactly(cuda_lib):
+    # x row m is one-hot at k_m: y[m, n] = w[n, k_m] with no summation (the other K slices add exact
+    # zeros), so the result must equal the reference's dequantised weight bit for bit
+    n, k = 256, 1024
+    rng = np.random.default_rng(23)
+    wq, s = synth.make_weights(n, k, rng)
+    w = oracle.c_dequantize(wq, s)
+    for base in range(0, k, 128):
+        x = np.zeros((128, k), np.float16)
+        x[np.arange(128), base + np.arange(128)] = 1.0
+        out = run_matmul(x, wq, s, family="gemm_ws")
+        assert_bits_equal(out, w[:, base:base + 128].T.copy(), f"one-hot rows at {base}")
+    assert cuda_lib.b200_device_error_flags() == 0
+
+
+def test_gemm_ws_rejects_what_it_cannot_take(cuda_lib):
+    x, wq, s = synth.make_case(129, 64, 256, seed=1)
+    tx, twq, ts = dev(x, wq, s)
+    y = torch.empty((129, 64), dtype=torch.float16, device="cuda")
+    assert cuda_lib.b200_q4f16_gemm_ws(tx.data_ptr(), twq.data_ptr(), ts.data_ptr(), y.data_ptr(), 129, 64, 256, 0) == _lib.EINVAL
+    x, wq, s = synth.make_case(32, 64, 96, seed=1)       # K not a multiple of 256
+    tx, twq, ts = dev(x, wq, s)
+    assert cuda_lib.b200_q4f16_gemm_ws(tx.data_ptr(), twq.data_ptr(), ts.data_ptr(), y.data_ptr(), 32, 64, 96, 0) == _lib.EINVAL
+
+
+@pytest.mark.parametrize("m", [17, 48, 128, 129, 200])
+def test_auto_dispatch_mid_batches(cuda_lib, m):
+    # 16 < M <= 128 goes to the weight-stationary kernel, above that to the prefill kernel; both must agree with the oracle
+    x, wq, s = synth.make_case(m, 768, 1024, seed=m)
+    assert_matmul_close(run_matmul(x, wq, s), x, wq, s, f"auto M={m}")
+    assert cuda_lib.b200_device_error_flags() == 0
