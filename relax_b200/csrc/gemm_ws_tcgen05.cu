@@ -40,44 +40,38 @@ using namespace ptx;
 constexpr int BR = 128;            // weight rows per tile (UMMA M)
 constexpr int BK = 64;             // k per MMA stage (one 128-byte swizzled row of fp16)
 constexpr int kMaxNB = 128;        // batch columns (UMMA N), multiple of 16
-constexpr int SX = 4;              // x stages
-constexpr int SW = 3;              // dequantised-weight stages
-constexpr int SR = 3;              // packed-weight stages (128 k each = two K blocks)
-constexpr int SS = 2;              // scale stages (256 k each = four K blocks)
-constexpr int kWBytes = BR * BK * 2;          // 16384
-constexpr int kXBytesMax = kMaxNB * BK * 2;   // 16384
-constexpr int kRawBytes = BR * 64;            // 8192: 128 rows x 16 words
-constexpr int kScBytes = BR * 16;             // 2048: 128 rows x 8 scales
+constexpr int kMaxStages = 8;
+constexpr int kWBytes = BR * BK * 2;          // 16384: one dequantised K block
+constexpr int kRawBytes = BR * 64 * 2;        // 16384: 128 rows x 32 words = 256 k = four K blocks
+constexpr int kScBytes = BR * 16;             // 2048:  128 rows x 8 scales  = 256 k
 constexpr int kNumThreads = 512;
 constexpr int kDequantWarps = 8;
 constexpr uint64_t kWaitNs = 4000000000ull;   // 4 s
 
-struct Smem {
-  // all operand buffers are multiples of 1024 bytes, the struct is placed 1024-aligned
-  unsigned char w[SW][kWBytes];
-  unsigned char x[SX][kXBytesMax];
-  unsigned char raw[SR][kRawBytes];
-  unsigned char sc[SS][kScBytes];
-  float part[kMaxNB * BR];                      // this CTA's partial tile, [batch column][weight row]
-  uint64_t x_full[SX], x_empty[SX];
-  uint64_t w_full[SW], w_empty[SW];
-  uint64_t raw_full[SR], raw_empty[SR];
-  uint64_t sc_full[SS], sc_empty[SS];
-  uint64_t acc_full;
-  uint32_t tmem_base;
-  int abort_flag;
-};
-
+// A single thread sustains only ~2 tiled TMA loads per microsecond whatever their size, so every
+// load carries several K blocks (3-D boxes: the K block is the outer coordinate) and the three
+// kinds of load are issued by three different warps.
 struct WsParams {
-  CUtensorMap tm_x;    // fp16   {K, M},     box {64, NB},   SWIZZLE_128B
-  CUtensorMap tm_w;    // uint32 {K/8, N},   box {16, 128},  SWIZZLE_64B
-  CUtensorMap tm_s;    // fp16   {K/32, N},  box {8, 128}
+  CUtensorMap tm_x;    // fp16   {64, M, K/64},    box {64, NB, XK},   SWIZZLE_128B: [K block][batch row][128 B]
+  CUtensorMap tm_w;    // uint32 {16, N, K/128},   box {16, 128, 2},   SWIZZLE_64B:  [128-k half][row][64 B]
+  CUtensorMap tm_s;    // fp16   {K/32, N},        box {8, 128}
   __half* y;
   int M, N, K;
   int NB;              // batch columns of the MMA: M rounded up to 16
+  int XK;              // K blocks per x load (2 or 4)
+  int SX, SW, SR;      // ring depths: x loads, dequantised K blocks, packed 256-k spans (weights + scales)
   int ksplit;          // CTAs per cluster = K slices
   int kb_total;        // K / 64
   uint32_t tmem_cols;  // power of two >= max(32, NB)
+};
+
+struct Bars {
+  uint64_t x_full[kMaxStages], x_empty[kMaxStages];
+  uint64_t w_full[kMaxStages], w_empty[kMaxStages];
+  uint64_t r_full[kMaxStages], r_empty[kMaxStages];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
 };
 
 __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
@@ -88,11 +82,40 @@ __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
 }
 
+// Position in a ring of `n` stages without divisions (the ring depths are run-time values and a
+// single issuing thread cannot afford integer divisions per K block): stage index + wrap parity.
+struct Ring {
+  int s = 0;
+  uint32_t phase = 0;      // number of completed wraps, mod 2
+  bool wrapped = false;    // at least one wrap so far
+  __device__ __forceinline__ void next(int n) {
+    if (++s == n) { s = 0; phase ^= 1; wrapped = true; }
+  }
+};
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, int32_t c0, int32_t c1, int32_t c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Shared memory (1024-aligned base): x ring [SX][XK][NB][128 B] | w ring [SW][16 KB] | raw ring [SR][16 KB]
+// | scale ring [SR][2 KB] | barriers.  After the main loop the x ring is reused for this CTA's
+// partial tile [batch column][weight row] fp32 (NB * 512 B <= SX * XK * NB * 128 B since XK >= 2, SX >= 2).
 __global__ void __launch_bounds__(kNumThreads, 1)
 q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
   extern __shared__ unsigned char smem_unaligned[];
-  Smem& sm = *reinterpret_cast<Smem*>(smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u));
-  volatile int* abort_flag = &sm.abort_flag;
+  unsigned char* base = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+  const int xstage = p.XK * p.NB * 128;
+  unsigned char* x_ring = base;
+  unsigned char* w_ring = x_ring + (size_t)p.SX * xstage;
+  unsigned char* raw_ring = w_ring + (size_t)p.SW * kWBytes;
+  unsigned char* sc_ring = raw_ring + (size_t)p.SR * kRawBytes;
+  Bars& bar = *reinterpret_cast<Bars*>(sc_ring + (size_t)p.SR * kScBytes);
+  float* part = reinterpret_cast<float*>(x_ring);
+  volatile int* abort_flag = &bar.abort_flag;
   cg::cluster_group cluster = cg::this_cluster();
 
   const int tid = threadIdx.x;
@@ -100,57 +123,58 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
   const int lane = tid & 31;
   const int krank = (int)cluster.block_rank();          // K slice of this CTA (gridDim.x == ksplit)
   const int row0 = blockIdx.y * BR;
-  // K blocks of 64, handed out in units of 4 (= one scale stage of 256 k), the first slices one unit longer
+  // K blocks of 64, handed out in units of 4 (= one 256-k span), the first slices one unit longer
   const int units = p.kb_total >> 2;
   const int ubase = units / p.ksplit, uextra = units % p.ksplit;
   const int u0 = krank * ubase + min(krank, uextra);
   const int kb0 = u0 * 4;
   const int num_kb = (ubase + (krank < uextra ? 1 : 0)) * 4;
-  const int xbytes = p.NB * BK * 2;
 
   if (tid == 0) {
-    sm.abort_flag = 0;
-    for (int i = 0; i < SX; ++i) { mbar_init(&sm.x_full[i], 1); mbar_init(&sm.x_empty[i], 1); }
-    for (int i = 0; i < SW; ++i) { mbar_init(&sm.w_full[i], kDequantWarps); mbar_init(&sm.w_empty[i], 1); }
-    for (int i = 0; i < SR; ++i) { mbar_init(&sm.raw_full[i], 1); mbar_init(&sm.raw_empty[i], kDequantWarps); }
-    for (int i = 0; i < SS; ++i) { mbar_init(&sm.sc_full[i], 1); mbar_init(&sm.sc_empty[i], kDequantWarps); }
-    mbar_init(&sm.acc_full, 1);
+    bar.abort_flag = 0;
+    for (int i = 0; i < kMaxStages; ++i) {
+      mbar_init(&bar.x_full[i], 1); mbar_init(&bar.x_empty[i], 1);
+      mbar_init(&bar.w_full[i], kDequantWarps); mbar_init(&bar.w_empty[i], 1);
+      mbar_init(&bar.r_full[i], 2); mbar_init(&bar.r_empty[i], kDequantWarps);
+    }
+    mbar_init(&bar.acc_full, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&sm.tmem_base, p.tmem_cols);
+    tmem_alloc(&bar.tmem_base, p.tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = sm.tmem_base;
+  const uint32_t tmem_base = bar.tmem_base;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer: x (XK K blocks per load)
     if (lane == 0) {
       prefetch_tmap(&p.tm_x);
-      prefetch_tmap(&p.tm_w);
-      prefetch_tmap(&p.tm_s);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int gk = kb0 + kb;                       // global K block
-        if ((kb & 3) == 0) {
-          const int it = kb >> 2, s = it % SS;
-          if (it >= SS) wait_or_abort(&sm.sc_empty[s], ((it / SS) - 1) & 1, abort_flag, 2);
-          mbar_arrive_expect_tx(&sm.sc_full[s], kScBytes);
-          tma_load_2d(sm.sc[s], &p.tm_s, (gk >> 2) * 8, row0, &sm.sc_full[s]);
-        }
-        if ((kb & 1) == 0) {
-          const int it = kb >> 1, s = it % SR;
-          if (it >= SR) wait_or_abort(&sm.raw_empty[s], ((it / SR) - 1) & 1, abort_flag, 3);
-          mbar_arrive_expect_tx(&sm.raw_full[s], kRawBytes);
-          tma_load_2d(sm.raw[s], &p.tm_w, (gk >> 1) * 16, row0, &sm.raw_full[s]);
-        }
-        {
-          const int s = kb % SX;
-          if (kb >= SX) wait_or_abort(&sm.x_empty[s], ((kb / SX) - 1) & 1, abort_flag, 1);
-          mbar_arrive_expect_tx(&sm.x_full[s], xbytes);
-          tma_load_2d(sm.x[s], &p.tm_x, gk * BK, 0, &sm.x_full[s]);
+      Ring rx;
+      for (int kb = 0; kb < num_kb; kb += p.XK, rx.next(p.SX)) {
+        if (rx.wrapped) wait_or_abort(&bar.x_empty[rx.s], rx.phase ^ 1, abort_flag, 1);
+        mbar_arrive_expect_tx(&bar.x_full[rx.s], xstage);
+        tma_load_3d(x_ring + (size_t)rx.s * xstage, &p.tm_x, 0, 0, kb0 + kb, &bar.x_full[rx.s]);
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    // ------------------------------------------------------------------ TMA producers: packed weights (warp 2), scales (warp 3), 256 k per load
+    if (lane == 0) {
+      prefetch_tmap(warp == 2 ? &p.tm_w : &p.tm_s);
+      Ring rr;
+      for (int kb = 0; kb < num_kb; kb += 4, rr.next(p.SR)) {
+        const int s = rr.s;
+        const int gk = kb0 + kb;
+        if (rr.wrapped) wait_or_abort(&bar.r_empty[s], rr.phase ^ 1, abort_flag, 3);
+        if (warp == 2) {
+          mbar_arrive_expect_tx(&bar.r_full[s], kRawBytes);
+          tma_load_3d(raw_ring + (size_t)s * kRawBytes, &p.tm_w, 0, row0, gk >> 1, &bar.r_full[s]);
+        } else {
+          mbar_arrive_expect_tx(&bar.r_full[s], kScBytes);
+          tma_load_2d(sc_ring + (size_t)s * kScBytes, &p.tm_s, (gk >> 2) * 8, row0, &bar.r_full[s]);
         }
       }
     }
@@ -158,25 +182,99 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16_f32(BR, p.NB);
+      Ring rx, rw;
+      int xslab = 0;
       for (int kb = 0; kb < num_kb; ++kb) {
-        const int sx = kb % SX, sw = kb % SW;
-        wait_or_abort(&sm.x_full[sx], (kb / SX) & 1, abort_flag, 5);
-        wait_or_abort(&sm.w_full[sw], (kb / SW) & 1, abort_flag, 6);
+        const int sx = rx.s, sw = rw.s;
+        if (xslab == 0) wait_or_abort(&bar.x_full[sx], rx.phase, abort_flag, 5);
+        wait_or_abort(&bar.w_full[sw], rw.phase, abort_flag, 6);
         tc_fence_after_sync();
-        const uint64_t da = umma_desc_k128(smem_u32(sm.w[sw]));
-        const uint64_t db = umma_desc_k128(smem_u32(sm.x[sx]));
+        const uint64_t da = umma_desc_k128(smem_u32(w_ring + (size_t)sw * kWBytes));
+        const uint64_t db = umma_desc_k128(smem_u32(x_ring + (size_t)sx * xstage + (size_t)xslab * p.NB * 128));
 #pragma unroll
         for (int k16 = 0; k16 < BK / 16; ++k16)
           umma_f16_ss(tmem_base, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, (kb | k16) != 0);
-        umma_commit(&sm.x_empty[sx]);
-        umma_commit(&sm.w_empty[sw]);
+        umma_commit(&bar.w_empty[sw]);
+        rw.next(p.SW);
+        if (++xslab == p.XK) {
+          umma_commit(&bar.x_empty[sx]);
+          xslab = 0;
+          rx.next(p.SX);
+        }
       }
-      umma_commit(&sm.acc_full);
+      umma_commit(&bar.acc_full);
     }
-  } else if (warp >= 4 && warp < 8) {
-    // ------------------------------------------------------------------ epilogue, part 1: TMEM -> this CTA's partial tile
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ dequantisers
+    const int t = tid - 256;
+    const int r = t & 127;                          // weight row inside the tile
+    const int half = t >> 7;                        // which 32-k half (= scale group) of each K block
+    const int r8 = r & 7;
+    const int sx64 = (r >> 1) & 3;                  // 64-byte swizzle phase of row r
+    const Q4Consts qc = q4_consts();
+    Ring rr, rw;
+    for (int it = 0; it * 4 < num_kb; ++it, rr.next(p.SR)) {
+      const int s = rr.s;
+      wait_or_abort(&bar.r_full[s], rr.phase, abort_flag, 8);
+      // this thread's share of the 256-k span: one 16-byte chunk (4 words = one scale group) and
+      // one scale per K block.  Span layout: [128-k half h2][row][64 B]; K block j = half j>>1,
+      // chunks 2*(j&1), 2*(j&1)+1 of the row; scales: row r holds groups 0..7, K block j uses 2j, 2j+1.
+      uint4 pk[4];
+      uint32_t scb[4];
+      const unsigned char* rbase = raw_ring + (size_t)s * kRawBytes + r * 64;
+      const __half* srow = reinterpret_cast<const __half*>(sc_ring + (size_t)s * kScBytes + r * 16);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        pk[j] = *reinterpret_cast<const uint4*>(rbase + (j >> 1) * (BR * 64) + (((2 * (j & 1) + half) ^ sx64) << 4));
+        scb[j] = __half_as_ushort(srow[2 * j + half]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        pin_loaded(pk[j]);
+        pin_loaded(scb[j]);
+      }
+      fence_proxy_async_smem();              // generic reads ordered before the TMA refill (async proxy)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.r_empty[s]);
+      // G K blocks per round: one proxy fence and one round of arrivals for all of them (the fence
+      // costs hundreds of cycles; per K block it would set the pace of the whole pipeline)
+      const int G = p.SW >= 8 ? 4 : (p.SW >= 4 ? 2 : 1);
+      for (int j0 = 0; j0 < 4; j0 += G) {
+        int sws[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < j0 || j >= j0 + G) continue;
+          const int sw = rw.s;
+          sws[j] = sw;
+          if (rw.wrapped) wait_or_abort(&bar.w_empty[sw], rw.phase ^ 1, abort_flag, 10);
+          rw.next(p.SW);
+          const __half sch = __ushort_as_half((unsigned short)scb[j]);
+          const __half2 s2 = __half2(sch, sch);
+          unsigned char* wrow = w_ring + (size_t)sw * kWBytes + r * 128;   // 8-row atoms of 1024 B, rows 128 B apart
+          const uint32_t wd[4] = {pk[j].x, pk[j].y, pk[j].z, pk[j].w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 o = q4_dequant_natural(wd[c], s2, qc);
+            *reinterpret_cast<uint4*>(wrow + (((4 * half + c) ^ r8) << 4)) = o;
+          }
+        }
+        fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (j >= j0 && j < j0 + G) mbar_arrive(&bar.w_full[sws[j]]);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- TMEM -> this CTA's partial tile
+  if (warp >= 4 && warp < 8) {
     const int ew = warp - 4;                       // TMEM lane quadrant this warp may read
-    wait_or_abort(&sm.acc_full, 0, abort_flag, 7);
+    // acc_full is committed after every MMA (and with it every read of the x ring) has completed,
+    // so the x ring may now be overwritten with the partial tile
+    wait_or_abort(&bar.acc_full, 0, abort_flag, 7);
     tc_fence_after_sync();
     const int r = ew * 32 + lane;                  // weight row inside the tile = TMEM lane
     const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16);
@@ -186,65 +284,9 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
       tmem_ld_wait();
 #pragma unroll
       for (int q = 0; q < 32; ++q)
-        if (c0 + q < p.NB) sm.part[(c0 + q) * BR + r] = num_kb > 0 ? __uint_as_float(v[q]) : 0.f;
+        if (c0 + q < p.NB) part[(c0 + q) * BR + r] = num_kb > 0 ? __uint_as_float(v[q]) : 0.f;
     }
     tc_fence_before_sync();
-  } else if (warp >= 8) {
-    // ------------------------------------------------------------------ dequantisers
-    const int t = tid - 256;
-    const int r = t & 127;                          // weight row inside the tile
-    const int half = t >> 7;                        // which 32-k half (= scale group) of each K block
-    const int r8 = r & 7;
-    const Q4Consts qc = q4_consts();
-    uint4 pk[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};   // this thread's words of the two K blocks of a raw stage
-    uint32_t sc2[2] = {0, 0};                       // this thread's 4 scales of a scale stage (one per K block)
-    for (int kb = 0; kb < num_kb; ++kb) {
-      if ((kb & 3) == 0) {
-        const int it = kb >> 2, s = it % SS;
-        wait_or_abort(&sm.sc_full[s], (it / SS) & 1, abort_flag, 8);
-        // row r holds 8 scales (groups of this 256-k span); K block j of the span uses groups 2j, 2j+1
-        const __half* srow = reinterpret_cast<const __half*>(sm.sc[s] + r * 16);
-        const uint32_t a0 = __half_as_ushort(srow[0 + half]), a1 = __half_as_ushort(srow[2 + half]);
-        const uint32_t a2 = __half_as_ushort(srow[4 + half]), a3 = __half_as_ushort(srow[6 + half]);
-        sc2[0] = a0 | (a1 << 16);
-        sc2[1] = a2 | (a3 << 16);
-        pin_loaded(sc2[0]);
-        pin_loaded(sc2[1]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.sc_empty[s]);
-      }
-      if ((kb & 1) == 0) {
-        const int it = kb >> 1, s = it % SR;
-        wait_or_abort(&sm.raw_full[s], (it / SR) & 1, abort_flag, 9);
-        // row r holds 64 bytes = 4 chunks of 16 (chunk c = words 4c..4c+3); 64-byte swizzle: chunk ^= (r >> 1) & 3
-        const unsigned char* rr = sm.raw[s] + r * 64;
-        const int sx = (r >> 1) & 3;
-        pk[0] = *reinterpret_cast<const uint4*>(rr + (((0 + half) ^ sx) << 4));    // K block 0: chunks 0,1
-        pk[1] = *reinterpret_cast<const uint4*>(rr + (((2 + half) ^ sx) << 4));    // K block 1: chunks 2,3
-        pin_loaded(pk[0]);
-        pin_loaded(pk[1]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.raw_empty[s]);
-      }
-      const int sw = kb % SW;
-      if (kb >= SW) wait_or_abort(&sm.w_empty[sw], ((kb / SW) - 1) & 1, abort_flag, 10);
-      const uint32_t scw = sc2[(kb >> 1) & 1];
-      const __half sch = __ushort_as_half((unsigned short)((kb & 1) ? (scw >> 16) : (scw & 0xffffu)));
-      const __half2 s2 = __half2(sch, sch);
-      const uint4 words = pk[kb & 1];
-      unsigned char* wrow = sm.w[sw] + r * 128;       // 8-row atoms of 1024 B, rows 128 B apart
-      const uint32_t wd[4] = {words.x, words.y, words.z, words.w};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint4 o = q4_dequant_natural(wd[c], s2, qc);
-        *reinterpret_cast<uint4*>(wrow + (((4 * half + c) ^ r8) << 4)) = o;
-      }
-      fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.w_full[sw]);
-    }
   }
 
   // ---------------------------------------------------------------------- sum over the K slices
@@ -255,7 +297,7 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
     for (int c = krank; c < p.M; c += p.ksplit) {      // this CTA's batch columns
       float sum = 0.f;
       for (int q = 0; q < p.ksplit; ++q) {
-        const float* remote = cluster.map_shared_rank(sm.part, q);
+        const float* remote = cluster.map_shared_rank(part, q);
         sum += remote[c * BR + r];
       }
       if (row < p.N) p.y[(int64_t)c * p.N + row] = __float2half_rn(sum);
@@ -285,17 +327,18 @@ int launch_gemm_ws(const __half* x, const uint32_t* wq, const __half* scales, __
   WsParams p;
   int rc;
   p.NB = (int)((M + 15) / 16) * 16;
+  p.XK = p.NB <= 64 ? 4 : 2;
   {
-    const uint64_t d[2] = {(uint64_t)K, (uint64_t)M};
-    const uint64_t s[1] = {(uint64_t)K * 2};
-    const uint32_t b[2] = {BK, (uint32_t)p.NB};
-    if ((rc = make_tmap(&p.tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    const uint64_t d[3] = {BK, (uint64_t)M, (uint64_t)(K / BK)};
+    const uint64_t s[2] = {(uint64_t)K * 2, BK * 2};
+    const uint32_t b[3] = {BK, (uint32_t)p.NB, (uint32_t)p.XK};
+    if ((rc = make_tmap(&p.tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, x, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   }
   {
-    const uint64_t d[2] = {(uint64_t)(K / 8), (uint64_t)N};
-    const uint64_t s[1] = {(uint64_t)(K / 2)};
-    const uint32_t b[2] = {16, BR};
-    if ((rc = make_tmap(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, wq, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+    const uint64_t d[3] = {16, (uint64_t)N, (uint64_t)(K / 128)};
+    const uint64_t s[2] = {(uint64_t)(K / 2), 64};
+    const uint32_t b[3] = {16, BR, 2};
+    if ((rc = make_tmap(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, wq, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
   }
   {
     const uint64_t d[2] = {(uint64_t)(K / 32), (uint64_t)N};
@@ -317,7 +360,17 @@ int launch_gemm_ws(const __half* x, const uint32_t* wq, const __half* scales, __
   if (ksplit > units) ksplit = units;
   p.ksplit = ksplit;
 
-  const size_t smem = sizeof(Smem) + 1024;
+  // ring depths: three x loads and three packed spans in flight, the rest of the shared memory for
+  // dequantised K blocks (the deeper that ring, the less the dequantisers wait for the MMA's commits)
+  p.SX = 3;
+  p.SR = 3;
+  const size_t xstage = (size_t)p.XK * p.NB * 128;
+  const size_t fixed = 1024 + p.SX * xstage + p.SR * (size_t)(kRawBytes + kScBytes) + sizeof(Bars) + 256;
+  int sw = (int)((227 * 1024 - fixed) / kWBytes);
+  if (sw > kMaxStages) sw = kMaxStages;
+  if (sw < 2) return B200_ENOTREADY;
+  p.SW = sw;
+  const size_t smem = fixed + (size_t)p.SW * kWBytes;
   auto kern = q4f16_gemm_ws_tcgen05_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemm_ws: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
