@@ -114,8 +114,10 @@ int matmul_impl(Family fam, const char* who, const void* x, const void* wq, cons
   auto sh = static_cast<const __half*>(scales);
   auto yh = static_cast<__half*>(y);
   if (use_gemv) return launch_gemv(xh, wh, sh, yh, M, N, K, s);
-  if (fam == kGemmWs || (fam == kAuto && M <= options().gemm_ws_max_m)) {
-    // mid-sized batches: weights stream once through the weight-stationary kernel
+  // Mid-sized batches with few weight rows: the prefill kernel would have only N/256 tiles to spread
+  // over the SMs, the weight-stationary kernel splits K over a cluster instead (measured faster up to
+  // N of about 8192 on B200; beyond that the prefill kernel's tiles fill the GPU).
+  if (fam == kGemmWs || (fam == kAuto && M <= options().gemm_ws_max_m && N <= 8192)) {
     rc = launch_gemm_ws(xh, wh, sh, yh, M, N, K, s);
     if (rc != B200_ENOTREADY) return rc;
     if (fam == kGemmWs) return fail(B200_EINVAL, "%s: the weight-stationary kernel takes 1 <= M <= 128, K %% 256 == 0, 16-byte aligned scales", who);

@@ -59,7 +59,8 @@ struct WsParams {
   int M, N, K;
   int NB;              // batch columns of the MMA: M rounded up to 16
   int XK;              // K blocks per x load (2 or 4)
-  int SX, SW, SR;      // ring depths: x loads, dequantised K blocks, packed 256-k spans (weights + scales)
+  int WK;              // K blocks per dequantised-weight stage (4 or 2): one hand-shake with the MMA thread per stage
+  int SX, SW, SR;      // ring depths: x loads, dequantised stages, packed 256-k spans (weights + scales)
   int ksplit;          // CTAs per cluster = K slices
   int kb_total;        // K / 64
   uint32_t tmem_cols;  // power of two >= max(32, NB)
@@ -101,7 +102,7 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, in
       : "memory");
 }
 
-// Shared memory (1024-aligned base): x ring [SX][XK][NB][128 B] | w ring [SW][16 KB] | raw ring [SR][16 KB]
+// Shared memory (1024-aligned base): x ring [SX][XK][NB][128 B] | w ring [SW][WK][16 KB] | raw ring [SR][16 KB]
 // | scale ring [SR][2 KB] | barriers.  After the main loop the x ring is reused for this CTA's
 // partial tile [batch column][weight row] fp32 (NB * 512 B <= SX * XK * NB * 128 B since XK >= 2, SX >= 2).
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -111,7 +112,8 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
   const int xstage = p.XK * p.NB * 128;
   unsigned char* x_ring = base;
   unsigned char* w_ring = x_ring + (size_t)p.SX * xstage;
-  unsigned char* raw_ring = w_ring + (size_t)p.SW * kWBytes;
+  const int wstage = p.WK * kWBytes;
+  unsigned char* raw_ring = w_ring + (size_t)p.SW * wstage;
   unsigned char* sc_ring = raw_ring + (size_t)p.SR * kRawBytes;
   Bars& bar = *reinterpret_cast<Bars*>(sc_ring + (size_t)p.SR * kScBytes);
   float* part = reinterpret_cast<float*>(x_ring);
@@ -182,25 +184,30 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16_f32(BR, p.NB);
+      // The issuing thread is the pace-maker when the batch is narrow (an MMA of N = 16 is short):
+      // one wait and one commit per stage of WK K blocks, descriptors advanced by constants.
       Ring rx, rw;
       int xslab = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int sx = rx.s, sw = rw.s;
-        if (xslab == 0) wait_or_abort(&bar.x_full[sx], rx.phase, abort_flag, 5);
-        wait_or_abort(&bar.w_full[sw], rw.phase, abort_flag, 6);
-        tc_fence_after_sync();
-        const uint64_t da = umma_desc_k128(smem_u32(w_ring + (size_t)sw * kWBytes));
-        const uint64_t db = umma_desc_k128(smem_u32(x_ring + (size_t)sx * xstage + (size_t)xslab * p.NB * 128));
-#pragma unroll
-        for (int k16 = 0; k16 < BK / 16; ++k16)
-          umma_f16_ss(tmem_base, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, (kb | k16) != 0);
-        umma_commit(&bar.w_empty[sw]);
-        rw.next(p.SW);
-        if (++xslab == p.XK) {
-          umma_commit(&bar.x_empty[sx]);
-          xslab = 0;
-          rx.next(p.SX);
+      uint32_t first = 0;                               // 0 until the first MMA has been issued
+      for (int kb = 0; kb < num_kb; kb += p.WK, rw.next(p.SW)) {
+        wait_or_abort(&bar.w_full[rw.s], rw.phase, abort_flag, 6);
+        uint64_t da = umma_desc_k128(smem_u32(w_ring + (size_t)rw.s * wstage));
+        for (int j = 0; j < p.WK; ++j, da += (uint64_t)(kWBytes >> 4)) {
+          if (xslab == 0) wait_or_abort(&bar.x_full[rx.s], rx.phase, abort_flag, 5);
+          tc_fence_after_sync();
+          const uint64_t db = umma_desc_k128(smem_u32(x_ring + (size_t)rx.s * xstage + (size_t)xslab * p.NB * 128));
+          umma_f16_ss(tmem_base, da, db, idesc, first);
+          first = 1;
+          umma_f16_ss(tmem_base, da + 2, db + 2, idesc, 1);
+          umma_f16_ss(tmem_base, da + 4, db + 4, idesc, 1);
+          umma_f16_ss(tmem_base, da + 6, db + 6, idesc, 1);
+          if (++xslab == p.XK) {
+            umma_commit(&bar.x_empty[rx.s]);
+            xslab = 0;
+            rx.next(p.SX);
+          }
         }
+        umma_commit(&bar.w_empty[rw.s]);
       }
       umma_commit(&bar.acc_full);
     }
@@ -236,21 +243,16 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
       fence_proxy_async_smem();              // generic reads ordered before the TMA refill (async proxy)
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar.r_empty[s]);
-      // G K blocks per round: one proxy fence and one round of arrivals for all of them (the fence
-      // costs hundreds of cycles; per K block it would set the pace of the whole pipeline)
-      const int G = p.SW >= 8 ? 4 : (p.SW >= 4 ? 2 : 1);
-      for (int j0 = 0; j0 < 4; j0 += G) {
-        int sws[4] = {0, 0, 0, 0};
+      // one dequantised stage = WK K blocks: one wait, one proxy fence and one arrival per stage
+      for (int j0 = 0; j0 < 4; j0 += p.WK, rw.next(p.SW)) {
+        if (rw.wrapped) wait_or_abort(&bar.w_empty[rw.s], rw.phase ^ 1, abort_flag, 10);
+        unsigned char* wst = w_ring + (size_t)rw.s * wstage + r * 128;     // 8-row atoms of 1024 B, rows 128 B apart
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          if (j < j0 || j >= j0 + G) continue;
-          const int sw = rw.s;
-          sws[j] = sw;
-          if (rw.wrapped) wait_or_abort(&bar.w_empty[sw], rw.phase ^ 1, abort_flag, 10);
-          rw.next(p.SW);
+          if (j < j0 || j >= j0 + p.WK) continue;
           const __half sch = __ushort_as_half((unsigned short)scb[j]);
           const __half2 s2 = __half2(sch, sch);
-          unsigned char* wrow = w_ring + (size_t)sw * kWBytes + r * 128;   // 8-row atoms of 1024 B, rows 128 B apart
+          unsigned char* wrow = wst + (j - j0) * kWBytes;
           const uint32_t wd[4] = {pk[j].x, pk[j].y, pk[j].z, pk[j].w};
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -260,11 +262,7 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
         }
         fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (j >= j0 && j < j0 + G) mbar_arrive(&bar.w_full[sws[j]]);
-        }
+        if (lane == 0) mbar_arrive(&bar.w_full[rw.s]);
       }
     }
   }
@@ -360,17 +358,18 @@ int launch_gemm_ws(const __half* x, const uint32_t* wq, const __half* scales, __
   if (ksplit > units) ksplit = units;
   p.ksplit = ksplit;
 
-  // ring depths: three x loads and three packed spans in flight, the rest of the shared memory for
-  // dequantised K blocks (the deeper that ring, the less the dequantisers wait for the MMA's commits)
-  p.SX = 3;
-  p.SR = 3;
+  // ring depths: the dequantised ring gets what the x ring and the packed ring leave
+  p.WK = p.NB <= 16 ? 4 : 2;
+  p.SX = p.NB <= 64 ? 3 : 2;
+  p.SR = p.NB <= 64 ? 3 : 2;
   const size_t xstage = (size_t)p.XK * p.NB * 128;
+  const size_t wstage = (size_t)p.WK * kWBytes;
   const size_t fixed = 1024 + p.SX * xstage + p.SR * (size_t)(kRawBytes + kScBytes) + sizeof(Bars) + 256;
-  int sw = (int)((227 * 1024 - fixed) / kWBytes);
-  if (sw > kMaxStages) sw = kMaxStages;
+  int sw = (int)((227 * 1024 - fixed) / wstage);
+  if (sw > 4) sw = 4;
   if (sw < 2) return B200_ENOTREADY;
   p.SW = sw;
-  const size_t smem = fixed + (size_t)p.SW * kWBytes;
+  const size_t smem = fixed + (size_t)p.SW * wstage;
   auto kern = q4f16_gemm_ws_tcgen05_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemm_ws: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
