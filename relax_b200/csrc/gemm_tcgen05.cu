@@ -15,7 +15,7 @@
 //   warp 2      TMA producer for the packed weights (box {16 words = 128 k, 256 rows}, 64-byte
 //               swizzle) and, when the scale rows are 16-byte aligned, for the scales (box
 //               {8 groups = 256 k, 256 rows}) -> rings RAW / SC
-//   warps 8-15  dequantisers: thread r owns weight row r of the tile.  Per K block it turns 8
+//   warps 8-23  dequantisers (two groups of 8 warps on alternate K blocks): thread r owns weight row r of the tile.  Per K block it turns 8
 //               packed words into 64 fp16 (exact q-7, one HMUL2 by the scale: the reference's
 //               rounding) and stores them as the 128-byte row r of the UMMA operand tile, chunk
 //               c at position c ^ (r % 8): the canonical K-major SWIZZLE_128B layout a TMA load
@@ -57,8 +57,9 @@ constexpr int kABytes = BMT * BK * 2;         // 32768: half h at +h*16384
 constexpr int kBBytes = BN * BK * 2;          // 32768
 constexpr int kRawBytes = BN * 64;            // 16384: 256 rows x 16 words
 constexpr int kScBytes = BN * 16;             // 4096:  256 rows x 8 scales
-constexpr int kNumThreads = 512;
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 8;          // per group; two groups take alternate K blocks
+constexpr int kDequantGroups = 2;
+constexpr int kNumThreads = 256 + kDequantGroups * kDequantWarps * 32;   // 768
 constexpr uint32_t kTmemCols = 512;
 constexpr uint64_t kWaitNs = 4000000000ull;   // 4 s
 
@@ -150,8 +151,8 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     sm.abort_flag = 0;
     for (int i = 0; i < SA; ++i) { mbar_init(&sm.a_full[i], 1); mbar_init(&sm.a_empty[i], 1); }
     for (int i = 0; i < SB; ++i) { mbar_init(&sm.b_full[i], kDequantWarps); mbar_init(&sm.b_empty[i], 1); }
-    for (int i = 0; i < SR; ++i) { mbar_init(&sm.raw_full[i], 1); mbar_init(&sm.raw_empty[i], kDequantWarps); }
-    for (int i = 0; i < SS; ++i) { mbar_init(&sm.sc_full[i], 1); mbar_init(&sm.sc_empty[i], kDequantWarps); }
+    for (int i = 0; i < SR; ++i) { mbar_init(&sm.raw_full[i], 1); mbar_init(&sm.raw_empty[i], kDequantGroups * kDequantWarps); }
+    for (int i = 0; i < SS; ++i) { mbar_init(&sm.sc_full[i], 1); mbar_init(&sm.sc_empty[i], kDequantGroups * kDequantWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 4); }
     mbar_fence_init();
   }
@@ -293,7 +294,12 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ dequantisers
-    const int r = tid - 256;                        // weight row inside the tile, 0..255
+    // Two groups of 8 warps; group g converts the K blocks whose running index is g mod 2 (= ring
+    // stage g of the dequantised operand), so two K blocks are in conversion at any time and the
+    // wait -> convert -> fence -> arrive latency of one overlaps the other's.  Both groups take part
+    // in the hand-shake of every packed / scale stage.
+    const int grp = (tid - 256) >> 8;
+    const int r = (tid - 256) & 255;                // weight row inside the tile, 0..255
     const int r8 = r & 7;
     const Q4Consts qc = q4_consts();
     uint32_t it_raw = 0, it_sc = 0, it_b = 0;
@@ -302,7 +308,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       const int tn = w.tn;
       const int grow = tn * BN + r;                 // global weight row (may be >= N: zero-filled)
       uint4 sc4 = make_uint4(0, 0, 0, 0);           // 8 scales of the current 256-k span
-      uint4 pk[4];                                  // 16 packed words of the current 128-k span
+      uint4 pa = make_uint4(0, 0, 0, 0), pb = pa;   // this group's 8 packed words of the current pair of K blocks
       for (int kb = 0; kb < num_kb; ++kb, ++it_b) {
         if ((kb & 3) == 0) {
           if (p.scales_tma) {
@@ -336,15 +342,18 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           // row r holds 64 bytes = 4 chunks of 16; 64-byte swizzle: chunk ^= (r >> 1) & 3
           const unsigned char* rr = sm.raw[s] + r * 64;
           const int x = (r >> 1) & 3;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rr + ((c ^ x) << 4));
-#pragma unroll
-          for (int c = 0; c < 4; ++c) pin_loaded(pk[c]);   // loads returned before the stage is released
+          // this group's K block of the pair (kb, kb+1) is the one whose running index has its parity
+          const int mine = ((it_b & 1) == (uint32_t)grp) ? 0 : 2;      // chunks 0,1 (kb) or 2,3 (kb+1)
+          pa = *reinterpret_cast<const uint4*>(rr + ((mine ^ x) << 4));
+          pb = *reinterpret_cast<const uint4*>(rr + (((mine + 1) ^ x) << 4));
+          pin_loaded(pa);                                  // loads returned before the stage is released
+          pin_loaded(pb);
           fence_proxy_async_smem();              // generic reads ordered before the TMA refill (async proxy)
           __syncwarp();
           if (lane == 0) mbar_arrive(&sm.raw_empty[s]);
           ++it_raw;
         }
+        if ((it_b & 1) != (uint32_t)grp) continue;   // the other group's K block
         // ---- this K block: words 8*(kb&1) .. +7 of pk, scale groups 2*(kb&3), 2*(kb&3)+1
         const int sb = it_b % SB;
         const uint32_t b_round = it_b / SB;
@@ -353,8 +362,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         const __half2 scp = u32_as_h2(scw);
         const __half2 s_lo = __half2(__low2half(scp), __low2half(scp));
         const __half2 s_hi = __half2(__high2half(scp), __high2half(scp));
-        const uint4 p0 = (kb & 1) ? pk[2] : pk[0];
-        const uint4 p1 = (kb & 1) ? pk[3] : pk[1];
+        const uint4 p0 = pa, p1 = pb;
         unsigned char* brow = sm.b[sb] + r * 128;     // 8-row atoms of 1024 B, rows 128 B apart
         const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
