@@ -13,8 +13,9 @@
 //   warp 0      TMA producer for x: box {64 k, 256 rows} fp16, 128-byte swizzle -> ring A
 //               (rows 0-127 and 128-255 of the box are the two halves' A operands)
 //   warp 2      TMA producer for the packed weights (box {16 words = 128 k, 256 rows}, 64-byte
-//               swizzle) and, when the scale rows are 16-byte aligned, for the scales (box
-//               {8 groups = 256 k, 256 rows}) -> rings RAW / SC
+//               swizzle) -> ring RAW.  The scales (16 bytes per row and 256 k) are read straight from
+//               global memory by the dequantisers, one span ahead: that leaves room for a third
+//               stage of the dequantised operand.
 //   warps 8-23  dequantisers (two groups of 8 warps on alternate K blocks): thread r owns weight row r of the tile.  Per K block it turns 8
 //               packed words into 64 fp16 (exact q-7, one HMUL2 by the scale: the reference's
 //               rounding) and stores them as the 128-byte row r of the UMMA operand tile, chunk
@@ -50,9 +51,8 @@ constexpr int BMT = 2 * BM;        // tokens per tile: two halves share each deq
 constexpr int BN = 256;            // weight rows per tile (UMMA N)
 constexpr int BK = 64;             // k per MMA stage (one 128-byte swizzled row of fp16)
 constexpr int SA = 3;              // x stages
-constexpr int SB = 2;              // dequantised-weight stages
+constexpr int SB = 3;              // dequantised-weight stages (the conversion of a K block runs ahead of the MMA of the one before)
 constexpr int SR = 2;              // packed-weight stages (128 k each = two K blocks)
-constexpr int SS = 2;              // scale stages (256 k each = four K blocks)
 constexpr int kABytes = BMT * BK * 2;         // 32768: half h at +h*16384
 constexpr int kBBytes = BN * BK * 2;          // 32768
 constexpr int kRawBytes = BN * 64;            // 16384: 256 rows x 16 words
@@ -68,11 +68,9 @@ struct Smem {
   unsigned char a[SA][kABytes];
   unsigned char b[SB][kBBytes];
   unsigned char raw[SR][kRawBytes];
-  unsigned char sc[SS][kScBytes];
   uint64_t a_full[SA], a_empty[SA];
   uint64_t b_full[SB], b_empty[SB];
   uint64_t raw_full[SR], raw_empty[SR];
-  uint64_t sc_full[SS], sc_empty[SS];
   uint64_t acc_full[2], acc_empty[2];   // one pair per half
   uint32_t tmem_base;
   int abort_flag;
@@ -81,12 +79,11 @@ struct Smem {
 struct GemmParams {
   CUtensorMap tm_x;    // fp16   {K, M},     box {64, 256}, SWIZZLE_128B
   CUtensorMap tm_w;    // uint32 {K/8, N},   box {16, 256}, SWIZZLE_64B
-  CUtensorMap tm_s;    // fp16   {K/32, N},  box {8, 256}   (only when scales_tma)
   const __half* scales;
   __half* y;
   int M, N, K;
   int tiles_m, tiles_n;
-  int scales_tma;
+  int scales_vec;      // scale rows are 16-byte aligned and whole 256-k spans: one 16-byte load per span
 };
 
 // Work units of one CTA, in order.  Whole waves of 256-token tiles first; if the last, partial
@@ -127,6 +124,23 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int i, Work& w) {
   return true;
 }
 
+// 8 scales (one 256-k span) of weight row `grow`; zero for rows >= N and groups past the end (a
+// zero scale makes the weight +-0).
+__device__ __forceinline__ uint4 load_scales(const GemmParams& p, int grow, int span) {
+  const int G = p.K >> 5;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (grow >= p.N || span * 8 >= G) return v;
+  const __half* srow = p.scales + (int64_t)grow * G + span * 8;
+  if (p.scales_vec) return __ldg(reinterpret_cast<const uint4*>(srow));
+  uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t bits = span * 8 + j < G ? (uint32_t)__half_as_ushort(__ldg(srow + j)) : 0u;
+    w[j >> 1] |= bits << (16 * (j & 1));
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Bounded wait that also honours (and raises) the block-wide abort flag.
 __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
   if (*abort_flag) return;
@@ -152,7 +166,6 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     for (int i = 0; i < SA; ++i) { mbar_init(&sm.a_full[i], 1); mbar_init(&sm.a_empty[i], 1); }
     for (int i = 0; i < SB; ++i) { mbar_init(&sm.b_full[i], kDequantWarps); mbar_init(&sm.b_empty[i], 1); }
     for (int i = 0; i < SR; ++i) { mbar_init(&sm.raw_full[i], 1); mbar_init(&sm.raw_empty[i], kDequantGroups * kDequantWarps); }
-    for (int i = 0; i < SS; ++i) { mbar_init(&sm.sc_full[i], 1); mbar_init(&sm.sc_empty[i], kDequantGroups * kDequantWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 4); }
     mbar_fence_init();
   }
@@ -185,20 +198,11 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ TMA producer: packed W, scales
     if (lane == 0) {
       prefetch_tmap(&p.tm_w);
-      if (p.scales_tma) prefetch_tmap(&p.tm_s);
-      uint32_t it_raw = 0, it_sc = 0;
+      uint32_t it_raw = 0;
       Work w;
       for (int i = 0; get_work(p, i, w); ++i) {
         const int tn = w.tn;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (p.scales_tma && (kb & 3) == 0) {
-            const int s = it_sc % SS;
-            const uint32_t round = it_sc / SS;
-            if (round > 0) wait_or_abort(&sm.sc_empty[s], (round - 1) & 1, abort_flag, 2);
-            mbar_arrive_expect_tx(&sm.sc_full[s], kScBytes);
-            tma_load_2d(sm.sc[s], &p.tm_s, (kb >> 2) * 8, tn * BN, &sm.sc_full[s]);
-            ++it_sc;
-          }
           if ((kb & 1) == 0) {
             const int s = it_raw % SR;
             const uint32_t round = it_raw / SR;
@@ -302,39 +306,20 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     const int r = (tid - 256) & 255;                // weight row inside the tile, 0..255
     const int r8 = r & 7;
     const Q4Consts qc = q4_consts();
-    uint32_t it_raw = 0, it_sc = 0, it_b = 0;
+    uint32_t it_raw = 0, it_b = 0;
     Work w;
     for (int i = 0; get_work(p, i, w); ++i) {
       const int tn = w.tn;
       const int grow = tn * BN + r;                 // global weight row (may be >= N: zero-filled)
       uint4 sc4 = make_uint4(0, 0, 0, 0);           // 8 scales of the current 256-k span
+      uint4 sc_next = load_scales(p, grow, 0);      // ... and of the next one
       uint4 pa = make_uint4(0, 0, 0, 0), pb = pa;   // this group's 8 packed words of the current pair of K blocks
       for (int kb = 0; kb < num_kb; ++kb, ++it_b) {
         if ((kb & 3) == 0) {
-          if (p.scales_tma) {
-            const int s = it_sc % SS;
-            wait_or_abort(&sm.sc_full[s], (it_sc / SS) & 1, abort_flag, 8);
-            sc4 = *reinterpret_cast<const uint4*>(sm.sc[s] + r * 16);
-            pin_loaded(sc4);
-            fence_proxy_async_smem();              // generic reads ordered before the TMA refill (async proxy)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.sc_empty[s]);
-            ++it_sc;
-          } else {
-            // scale rows not 16-byte aligned: plain loads, zero past the ends
-            const int G = p.K >> 5;
-            uint32_t w[4] = {0, 0, 0, 0};
-            if (grow < p.N) {
-              const __half* srow = p.scales + (int64_t)grow * G;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                int gi = (kb >> 2) * 8 + j;
-                uint32_t bits = gi < G ? (uint32_t)__half_as_ushort(__ldg(srow + gi)) : 0u;
-                w[j >> 1] |= bits << (16 * (j & 1));
-              }
-            }
-            sc4 = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          // the 8 scales of this row's next 256-k span come straight from global memory (L2): one
+          // 16-byte load per span and thread, fetched one span ahead of its use
+          sc4 = sc_next;
+          sc_next = load_scales(p, grow, (kb >> 2) + 1);
         }
         if ((kb & 1) == 0) {
           const int s = it_raw % SR;
@@ -410,15 +395,7 @@ int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __hal
     const uint32_t b[2] = {16, BN};
     if ((rc = make_tmap(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, wq, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
   }
-  p.scales_tma = (K % 256 == 0) && ((reinterpret_cast<uintptr_t>(scales) & 15u) == 0);
-  if (p.scales_tma) {
-    const uint64_t d[2] = {(uint64_t)(K / 32), (uint64_t)N};
-    const uint64_t s[1] = {(uint64_t)(K / 32) * 2};
-    const uint32_t b[2] = {8, BN};
-    if ((rc = make_tmap(&p.tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scales, d, s, b, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
-  } else {
-    p.tm_s = p.tm_w;   // unused
-  }
+  p.scales_vec = (K % 256 == 0) && ((reinterpret_cast<uintptr_t>(scales) & 15u) == 0);
   p.scales = scales;
   p.y = y;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
