@@ -109,6 +109,13 @@ int matmul_impl(Family fam, const char* who, const void* x, const void* wq, cons
   if (M == 0 || N == 0) return B200_OK;
   if (K == 0) return zero_output(y, M, N, s);
   bool use_gemv = fam == kGemv || (fam == kAuto && M <= 16);
+  // 9..16 batch rows with a long K: the skinny kernel would have to restage x in several K blocks
+  // (16 rows x K no longer fit beside its ring); the weight-stationary kernel streams x instead
+  if (fam == kAuto && M >= 9 && M <= 16 && M * K * 2 > 160 * 1024 && K % 256 == 0 && options().gemm_ws_max_m >= M) {
+    rc = launch_gemm_ws(static_cast<const __half*>(x), static_cast<const uint32_t*>(wq), static_cast<const __half*>(scales),
+                        static_cast<__half*>(y), M, N, K, s);
+    if (rc != B200_ENOTREADY) return rc;
+  }
   auto xh = static_cast<const __half*>(x);
   auto wh = static_cast<const uint32_t*>(wq);
   auto sh = static_cast<const __half*>(scales);

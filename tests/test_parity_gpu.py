@@ -366,3 +366,11 @@ def test_auto_dispatch_mid_batches(cuda_lib, m):
     x, wq, s = synth.make_case(m, 768, 1024, seed=m)
     assert_matmul_close(run_matmul(x, wq, s), x, wq, s, f"auto M={m}")
     assert cuda_lib.b200_device_error_flags() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(9, 512, 11008), (16, 1280, 8192), (12, 300, 16384)])
+def test_auto_dispatch_small_batch_long_k(cuda_lib, m, n, k):
+    # 9..16 rows whose x block does not fit beside the skinny kernel's ring go to the weight-stationary kernel
+    x, wq, s = synth.make_case(m, n, k, seed=m + k)
+    assert_matmul_close(run_matmul(x, wq, s), x, wq, s, f"auto M={m} K={k}")
+    assert cuda_lib.b200_device_error_flags() == 0
