@@ -150,6 +150,16 @@ __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
 }
 
+// Same for the roles that are off the critical path (TMA producers, epilogue warps): they sleep
+// between polls, so their polling does not take issue slots from the dequantisers.
+__device__ __forceinline__ void wait_or_abort_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (*abort_flag) return;
+  if (!mbar_wait_ns_relaxed(bar, parity, kWaitNs)) {
+    *abort_flag = 1;
+    atomicExch(&g_gemm_error, code);
+  }
+}
+
 __global__ void __launch_bounds__(kNumThreads, 1)
 q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ unsigned char smem_unaligned[];
@@ -188,7 +198,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % SA;
           const uint32_t round = it / SA;
-          if (round > 0) wait_or_abort(&sm.a_empty[s], (round - 1) & 1, abort_flag, 1);
+          if (round > 0) wait_or_abort_relaxed(&sm.a_empty[s], (round - 1) & 1, abort_flag, 1);
           mbar_arrive_expect_tx(&sm.a_full[s], kABytes);
           tma_load_2d(sm.a[s], &p.tm_x, kb * BK, w.tok0, &sm.a_full[s]);
         }
@@ -206,7 +216,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           if ((kb & 1) == 0) {
             const int s = it_raw % SR;
             const uint32_t round = it_raw / SR;
-            if (round > 0) wait_or_abort(&sm.raw_empty[s], (round - 1) & 1, abort_flag, 3);
+            if (round > 0) wait_or_abort_relaxed(&sm.raw_empty[s], (round - 1) & 1, abort_flag, 3);
             mbar_arrive_expect_tx(&sm.raw_full[s], kRawBytes);
             tma_load_2d(sm.raw[s], &p.tm_w, (kb >> 1) * 16, tn * BN, &sm.raw_full[s]);
             ++it_raw;
@@ -260,7 +270,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     for (int i = 0; get_work(p, i, w); ++i, ++it_tile) {
       const int tn = w.tn;
       for (int h = 0; h < 2; ++h) {
-        wait_or_abort(&sm.acc_full[h], it_tile & 1, abort_flag, 7);
+        wait_or_abort_relaxed(&sm.acc_full[h], it_tile & 1, abort_flag, 7);
         tc_fence_after_sync();
         const int row = w.tok0 + h * BM + ew * 32 + lane;
         const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)h * BN;

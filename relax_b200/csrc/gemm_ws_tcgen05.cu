@@ -83,6 +83,16 @@ __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
 }
 
+// Same for the roles that are off the critical path (TMA producers, epilogue warps): they sleep
+// between polls, so their polling does not take issue slots from the dequantisers.
+__device__ __forceinline__ void wait_or_abort_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (*abort_flag) return;
+  if (!mbar_wait_ns_relaxed(bar, parity, kWaitNs)) {
+    *abort_flag = 1;
+    atomicExch(&g_gemm_ws_error, code);
+  }
+}
+
 // Position in a ring of `n` stages without divisions (the ring depths are run-time values and a
 // single issuing thread cannot afford integer divisions per K block): stage index + wrap parity.
 struct Ring {
@@ -157,7 +167,7 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
       prefetch_tmap(&p.tm_x);
       Ring rx;
       for (int kb = 0; kb < num_kb; kb += p.XK, rx.next(p.SX)) {
-        if (rx.wrapped) wait_or_abort(&bar.x_empty[rx.s], rx.phase ^ 1, abort_flag, 1);
+        if (rx.wrapped) wait_or_abort_relaxed(&bar.x_empty[rx.s], rx.phase ^ 1, abort_flag, 1);
         mbar_arrive_expect_tx(&bar.x_full[rx.s], xstage);
         tma_load_3d(x_ring + (size_t)rx.s * xstage, &p.tm_x, 0, 0, kb0 + kb, &bar.x_full[rx.s]);
       }
@@ -170,7 +180,7 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
       for (int kb = 0; kb < num_kb; kb += 4, rr.next(p.SR)) {
         const int s = rr.s;
         const int gk = kb0 + kb;
-        if (rr.wrapped) wait_or_abort(&bar.r_empty[s], rr.phase ^ 1, abort_flag, 3);
+        if (rr.wrapped) wait_or_abort_relaxed(&bar.r_empty[s], rr.phase ^ 1, abort_flag, 3);
         if (warp == 2) {
           mbar_arrive_expect_tx(&bar.r_full[s], kRawBytes);
           tma_load_3d(raw_ring + (size_t)s * kRawBytes, &p.tm_w, 0, row0, gk >> 1, &bar.r_full[s]);
@@ -272,7 +282,7 @@ q4f16_gemm_ws_tcgen05_kernel(const __grid_constant__ WsParams p) {
     const int ew = warp - 4;                       // TMEM lane quadrant this warp may read
     // acc_full is committed after every MMA (and with it every read of the x ring) has completed,
     // so the x ring may now be overwritten with the partial tile
-    wait_or_abort(&bar.acc_full, 0, abort_flag, 7);
+    wait_or_abort_relaxed(&bar.acc_full, 0, abort_flag, 7);
     tc_fence_after_sync();
     const int r = ew * 32 + lane;                  // weight row inside the tile = TMEM lane
     const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16);
