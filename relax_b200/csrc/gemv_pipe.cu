@@ -452,7 +452,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
       // four items per thread and round: all loads of a round are issued before the first use
       const int words = p.kblk >> 3;
       const int items = words * NC;
-      constexpr int R = NC >= 8 ? 4 : 1;            // (registers: small batches keep two CTAs per SM)
+      constexpr int R = NC >= 8 ? 4 : (NC == 1 ? 2 : 1);   // (registers: small batches keep two CTAs per SM)
       for (int i0 = tid; i0 < items; i0 += kConsumers * R) {
         uint4 a[R], b[R], c[R];
         bool live[R];
