@@ -161,7 +161,6 @@ struct PipeParams {
   int ntiles;      // ceil(N / 16)
   int tiles_per_cta;
   // what the staging of x applies on the way in (the neighbours of the matmul in a decoder layer)
-  int prologue;              // kPrologueNone / kPrologueRmsNorm / kPrologueSwiGLU
   const __half* delta;       // RmsNorm: added to x first (or null)
   const __half* norm_w;      // RmsNorm: weight [K]
   __half* x_out;             // RmsNorm: fp16(x + delta) is written here by CTA 0 (or null)
@@ -177,7 +176,7 @@ struct PipeParams {
 //   accs: tiles_per_cta * MT*128*4 (only when K is cut into several blocks)
 //
 // Warps: CW consumers, then one TMA warp (two issuing lanes), then one epilogue warp.
-template <int NC, int CW, int CH>
+template <int NC, int CW, int CH, int PRO>
 __global__ void __launch_bounds__((CW + 2) * 32, 1)
 q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   constexpr int MT = (NC + 7) / 8;
@@ -398,7 +397,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   // CTA 0 also writes r out as the updated residual stream.
   __shared__ float s_part[16][CW];
   __shared__ float s_inv[16];
-  if (p.prologue == kPrologueRmsNorm) {
+  if (PRO == kPrologueRmsNorm) {
     // four rows at a time so that eight independent loads are in flight per thread
     constexpr int R = NC >= 8 ? 4 : 1;
     for (int m0 = 0; m0 < p.M; m0 += R) {
@@ -452,7 +451,8 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
       // four items per thread and round: all loads of a round are issued before the first use
       const int words = p.kblk >> 3;
       const int items = words * NC;
-      constexpr int R = NC >= 8 ? 4 : (NC == 1 ? 2 : 1);   // (registers: small batches keep two CTAs per SM)
+      // (registers: small batches keep two CTAs per SM; without a prologue only one array is live)
+      constexpr int R = NC >= 8 ? 4 : (PRO == kPrologueNone ? 4 : (NC == 1 ? 2 : 1));
       for (int i0 = tid; i0 < items; i0 += kConsumers * R) {
         uint4 a[R], b[R], c[R];
         bool live[R];
@@ -464,13 +464,13 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
           live[r] = i < items && m < p.M && k < p.K;
           a[r] = b[r] = c[r] = make_uint4(0, 0, 0, 0);
           if (live[r]) {
-            if (p.prologue == kPrologueSwiGLU) {
+            if (PRO == kPrologueSwiGLU) {
               // x is [M, 2K] = gate | up
               a[r] = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + k);
               b[r] = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * 2 * p.K + p.K + k);
             } else {
               a[r] = *reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K + k);
-              if (p.prologue == kPrologueRmsNorm) {
+              if (PRO == kPrologueRmsNorm) {
                 if (p.delta) b[r] = *reinterpret_cast<const uint4*>(p.delta + (int64_t)m * p.K + k);
                 c[r] = *reinterpret_cast<const uint4*>(p.norm_w + k);
               }
@@ -484,9 +484,9 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
           const int j = i / NC, m = i - j * NC;
           uint4 v = a[r];
           if (live[r]) {
-            if (p.prologue == kPrologueSwiGLU) {
+            if (PRO == kPrologueSwiGLU) {
               v = silu_mul_f16x8(a[r], b[r]);       // fp32 inside, one fp16 rounding
-            } else if (p.prologue == kPrologueRmsNorm) {
+            } else if (PRO == kPrologueRmsNorm) {
               if (p.delta) v = add_f16x8(v, b[r]);
               v = scale_f16x8(v, s_inv[m], c[r]);
             }
@@ -627,7 +627,7 @@ struct Prologue {
   float eps = 0.f;
 };
 
-template <int NC, int CW, int CH>
+template <int NC, int CW, int CH, int PRO>
 int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int M, int N, int K,
                 cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   constexpr int MT = (NC + 7) / 8;
@@ -650,7 +650,7 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   }
   p.x = x; p.y = y;
   p.M = M; p.N = N; p.K = K;
-  p.prologue = pro.kind; p.delta = pro.delta; p.norm_w = pro.norm_w; p.x_out = pro.x_out; p.eps = pro.eps;
+  p.delta = pro.delta; p.norm_w = pro.norm_w; p.x_out = pro.x_out; p.eps = pro.eps;
   p.red = red;
   p.ntiles = (N + kRows - 1) / kRows;
   const int kpad = ((K + KC - 1) / KC) * KC;
@@ -663,7 +663,7 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   if (stages > kMaxStages) stages = kMaxStages;
   const size_t kMaxSmem = 227 * 1024;
   const int sms = sm_count();
-  auto kern = q4f16_gemv_pipe_kernel<NC, CW, CH>;
+  auto kern = q4f16_gemv_pipe_kernel<NC, CW, CH, PRO>;
   // Ask for the largest shared-memory carve-out: the default picks the smallest that fits ONE CTA,
   // which would keep further CTAs (or the next dependent launch) off the SM.
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -730,22 +730,23 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   return B200_OK;
 }
 
-template <int CW, int CH>
+template <int CW, int CH, int PRO>
 int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int m, int n, int k,
                   cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
-  if (m == 1) return launch_pipe<1, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
-  if (m == 2) return launch_pipe<2, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
-  if (m <= 4) return launch_pipe<4, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
-  if (m <= 8) return launch_pipe<8, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
-  return launch_pipe<16, CW, CH>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m == 1) return launch_pipe<1, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m == 2) return launch_pipe<2, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m <= 4) return launch_pipe<4, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m <= 8) return launch_pipe<8, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
+  return launch_pipe<16, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
 }
 
 int dispatch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N, int64_t K,
                   cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   if (K % 256 != 0 || (reinterpret_cast<uintptr_t>(scales) & 15u)) return B200_ENOTREADY;
   int m = (int)M, n = (int)N, k = (int)K;
-  if (options().gemv_warps == 16) return launch_pipe_m<16, 16>(x, wq, scales, y, m, n, k, stream, pro, red);
-  return launch_pipe_m<8, 16>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (pro.kind == kPrologueRmsNorm) return launch_pipe_m<8, 16, kPrologueRmsNorm>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (pro.kind == kPrologueSwiGLU) return launch_pipe_m<8, 16, kPrologueSwiGLU>(x, wq, scales, y, m, n, k, stream, pro, red);
+  return launch_pipe_m<8, 16, kPrologueNone>(x, wq, scales, y, m, n, k, stream, pro, red);
 }
 
 PeerReduce make_reduce(const B200PeerReduce* r) {
