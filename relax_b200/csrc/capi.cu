@@ -177,6 +177,57 @@ int check_current_device(const char* who, int dev) {
 
 using namespace b200;
 
+// Small host transfers as kernels.  A copy-engine transfer on either side of a 5 us matmul costs
+// more than the matmul (each switch between the copy engine and the SMs is a few microseconds), so
+// activations and results up to kHostKernelBytes travel by a one-CTA-per-16-KB kernel that reads or
+// writes the pinned host buffer through its device mapping; the result copy is launched as a
+// programmatic dependent of the matmul.  Pageable host memory and larger transfers use cudaMemcpyAsync.
+namespace b200 {
+namespace {
+constexpr size_t kHostKernelBytes = 256 * 1024;
+
+__global__ void __launch_bounds__(256) host_copy_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                                                        size_t bytes, int wait_for_primary) {
+  if (wait_for_primary) asm volatile("griddepcontrol.wait;" ::: "memory");
+  const size_t n16 = bytes >> 4;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  if (blockIdx.x == 0)
+    for (size_t i = (n16 << 4) + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
+}
+
+// Device-side address of a pinned (page-locked, mapped) host buffer, or null for anything else.
+void* mapped_host_pointer(const void* host) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, host) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (a.type != cudaMemoryTypeHost) return nullptr;
+  return a.devicePointer;
+}
+
+// dst <- src (one of them a mapped host buffer) on `s`; dependent = launch as a programmatic dependent
+// of the kernel before it in the stream (the copy waits for that kernel's completion itself).
+int host_copy(const void* src, void* dst, size_t bytes, bool dependent, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((bytes + 16383) / 16384));
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, host_copy_kernel, static_cast<const unsigned char*>(src),
+                                     static_cast<unsigned char*>(dst), bytes, dependent ? 1 : 0);
+  if (e != cudaSuccess) return fail(B200_ELAUNCH, "q4f16_matmul_host: copy kernel: %s", cudaGetErrorString(e));
+  count_launch();
+  return B200_OK;
+}
+}  // namespace
+}  // namespace b200
+
 extern "C" {
 
 const char* b200_last_error(void) { return g_err; }
@@ -337,15 +388,26 @@ int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, cons
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if (M * K > 0) {
-    e = cudaMemcpyAsync(x_dev, x_host, (size_t)(M * K) * 2, cudaMemcpyHostToDevice, s);
-    if (e != cudaSuccess) return fail(B200_ELAUNCH, "q4f16_matmul_host: H2D copy: %s", cudaGetErrorString(e));
+  const size_t xb = (size_t)(M * K) * 2, yb = (size_t)(M * N) * 2;
+  if (xb > 0) {
+    void* xm = xb <= kHostKernelBytes && !(reinterpret_cast<uintptr_t>(x_host) & 15) ? mapped_host_pointer(x_host) : nullptr;
+    if (xm) {
+      if ((rc = host_copy(xm, x_dev, xb, false, s))) return rc;
+    } else {
+      e = cudaMemcpyAsync(x_dev, x_host, xb, cudaMemcpyHostToDevice, s);
+      if (e != cudaSuccess) return fail(B200_ELAUNCH, "q4f16_matmul_host: H2D copy: %s", cudaGetErrorString(e));
+    }
   }
   rc = matmul_impl(kAuto, "q4f16_matmul_host", x_dev, wq, scales, y_dev, M, N, K, stream);
   if (rc) return rc;
-  if (M * N > 0) {
-    e = cudaMemcpyAsync(y_host, y_dev, (size_t)(M * N) * 2, cudaMemcpyDeviceToHost, s);
-    if (e != cudaSuccess) return fail(B200_ELAUNCH, "q4f16_matmul_host: D2H copy: %s", cudaGetErrorString(e));
+  if (yb > 0) {
+    void* ym = yb <= kHostKernelBytes && !(reinterpret_cast<uintptr_t>(y_host) & 15) ? mapped_host_pointer(y_host) : nullptr;
+    if (ym) {
+      if ((rc = host_copy(y_dev, ym, yb, true, s))) return rc;
+    } else {
+      e = cudaMemcpyAsync(y_host, y_dev, yb, cudaMemcpyDeviceToHost, s);
+      if (e != cudaSuccess) return fail(B200_ELAUNCH, "q4f16_matmul_host: D2H copy: %s", cudaGetErrorString(e));
+    }
   }
   return B200_OK;
 }

@@ -192,19 +192,32 @@ def test_packed_entry_point_runs_on_device(cuda_lib):
     assert_matmul_close(ty.cpu().numpy(), x, wq, s, "packed")
 
 
-def test_host_buffer_entry_point(cuda_lib):
-    x, wq, s = synth.make_case(4, 256, 512, seed=9)
+@pytest.mark.parametrize("m,n,k,pinned", [
+    (4, 256, 512, True),        # pinned host buffers: the transfers run as kernels over the mapped buffers
+    (4, 256, 512, False),       # pageable host buffers: copy-engine transfers
+    (1, 4096, 4096, True),      # the benchmark shape
+    (3, 1001, 256, True),       # result size that is not a multiple of 16 bytes
+    (300, 512, 512, True),      # activations above the kernel-transfer limit, result below it
+    (64, 4096, 512, True),      # result above the limit
+])
+def test_host_buffer_entry_point(cuda_lib, m, n, k, pinned):
+    x, wq, s = synth.make_case(m, n, k, seed=9)
     _, twq, ts = dev(x, wq, s)
-    xh = torch.from_numpy(x).pin_memory()
-    yh = torch.empty((4, 256), dtype=torch.float16).pin_memory()
-    xd = torch.empty((4, 512), dtype=torch.float16, device="cuda")
-    yd = torch.empty((4, 256), dtype=torch.float16, device="cuda")
+    xh = torch.from_numpy(x)
+    yh = torch.zeros((m, n), dtype=torch.float16)
+    if pinned:
+        xh, yh = xh.pin_memory(), yh.pin_memory()
+    xd = torch.empty((m, k), dtype=torch.float16, device="cuda")
+    yd = torch.empty((m, n), dtype=torch.float16, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
-    rc = cuda_lib.b200_q4f16_matmul_host(xh.data_ptr(), xd.data_ptr(), twq.data_ptr(), ts.data_ptr(), yd.data_ptr(),
-                                         yh.data_ptr(), 4, 256, 512, st)
-    assert rc == 0, _lib.last_error()
+    for _ in range(2):          # twice: the second call's input transfer follows the first call's result transfer
+        rc = cuda_lib.b200_q4f16_matmul_host(xh.data_ptr(), xd.data_ptr(), twq.data_ptr(), ts.data_ptr(), yd.data_ptr(),
+                                             yh.data_ptr(), m, n, k, st)
+        assert rc == 0, _lib.last_error()
     torch.cuda.synchronize()
     assert_matmul_close(yh.numpy(), x, wq, s, "host buffers")
+    assert np.array_equal(yh.numpy().view(np.uint16), yd.cpu().numpy().view(np.uint16))
+    assert np.array_equal(xd.cpu().numpy().view(np.uint16), x.view(np.uint16))
 
 
 def test_launch_counter(cuda_lib):
