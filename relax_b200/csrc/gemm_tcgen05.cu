@@ -141,8 +141,11 @@ __device__ __forceinline__ uint4 load_scales(const GemmParams& p, int grow, int 
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Bounded wait that also honours (and raises) the block-wide abort flag.
+// Bounded wait that also honours (and raises) the block-wide abort flag.  The MMA thread runs
+// through here twice per K block: a barrier that has already completed costs one try_wait, not a
+// shared-memory read of the flag first (measured +4 % on the whole kernel).
 __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return;
   if (*abort_flag) return;
   if (!mbar_wait_ns(bar, parity, kWaitNs)) {
     *abort_flag = 1;
@@ -292,30 +295,36 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         const int row = w.tok0 + h * BM + ew * 32 + lane;
         const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)h * BN;
         if (h < w.nhalf && w.tok0 + h * BM < p.M) {  // (warp-uniform) half computed and holds real tokens
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr, v);
+          tmem_ld_wait();
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(taddr + c * 32, v);
-            tmem_ld_wait();
+            // pack this chunk, start the next chunk's TMEM load, then store: the load's latency
+            // overlaps the stores
+            uint4 o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              o[q].x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1])));
+              o[q].y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])));
+              o[q].z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])));
+              o[q].w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+            }
+            if (c + 1 < BN / 32) tmem_ld_32x32b_x32(taddr + (c + 1) * 32, v);
             const int col0 = tn * BN + c * 32;
             if (row < p.M && col0 < p.N) {
               __half* dst = p.y + (int64_t)row * p.N + col0;
               if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  uint4 o;
-                  o.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1])));
-                  o.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])));
-                  o.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])));
-                  o.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
-                  *reinterpret_cast<uint4*>(dst + 8 * q) = o;
-                }
+                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + 8 * q) = o[q];
               } else {
+                const __half* oh = reinterpret_cast<const __half*>(o);
 #pragma unroll
                 for (int q = 0; q < 32; ++q)
-                  if (col0 + q < p.N) dst[q] = __float2half_rn(__uint_as_float(v[q]));
+                  if (col0 + q < p.N) dst[q] = oh[q];
               }
             }
+            tmem_ld_wait();
           }
         }
         tc_fence_before_sync();

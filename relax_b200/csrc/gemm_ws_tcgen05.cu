@@ -76,6 +76,7 @@ struct Bars {
 };
 
 __device__ __forceinline__ void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return;   // completed barrier: no read of the flag on the fast path
   if (*abort_flag) return;
   if (!mbar_wait_ns(bar, parity, kWaitNs)) {
     *abort_flag = 1;
