@@ -63,21 +63,17 @@ class ClockSampler:
         self.proc = None
         self.lines = []
 
-    def _nvml_loop(self):
-        import pynvml as nv
+    def _nvml_sample(self):
+        nv, h = self.nv, self.nv_handle
+        self.nv_sm.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+        r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+        for name, bit in self.nv_bad.items():
+            if r & bit:
+                self.nv_reasons.add(name)
 
-        h = nv.nvmlDeviceGetHandleByIndex(self.index)
-        bad = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
-               "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
-               "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
-               "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
-        self.nv_max = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+    def _nvml_loop(self):
         while not self.stop_flag:
-            self.nv_sm.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-            for name, bit in bad.items():
-                if r & bit:
-                    self.nv_reasons.add(name)
+            self._nvml_sample()
             time.sleep(0.005)
 
     def start(self):
@@ -90,6 +86,15 @@ class ClockSampler:
             vis = os.environ.get("CUDA_VISIBLE_DEVICES")
             if vis and all(v.strip().isdigit() for v in vis.split(",")):
                 self.index = int(vis.split(",")[self.index])
+            # handle and limits are fetched here, before the timed region, so that the thread's first
+            # sample falls inside it even when the region lasts only tens of milliseconds
+            self.nv = nv
+            self.nv_handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.nv_bad = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                           "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                           "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                           "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+            self.nv_max = nv.nvmlDeviceGetMaxClockInfo(self.nv_handle, nv.NVML_CLOCK_SM)
             self.nv_thread = threading.Thread(target=self._nvml_loop, daemon=True)
             self.nv_thread.start()
             return
@@ -470,7 +475,7 @@ def main():
                     help="batch sizes of the decode measurement, e.g. 1,16")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"gemv": 1000, "prefill": 100}[args.workload] if args.impl == "b200" else 10
+        args.steps = {"gemv": 1000, "prefill": 300}[args.workload] if args.impl == "b200" else 10
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
