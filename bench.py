@@ -295,7 +295,7 @@ def run_decode(args, world, rank, dev, batch):
 # summarised under profiles/ (one capture per kernel change; not re-measured by this script).
 NCU_TRAFFIC_BYTES = {
     ("gemv", 1, 4096, 4096): 9485312,                  # reads only: the 8 KB result stays in L2
-    ("prefill", 2048, 11008, 4096): 42210048 + 3086080,  # most of the 45 MB result is still in L2 at kernel end
+    ("prefill", 2048, 11008, 4096): 42226944 + 3235328,  # most of the 45 MB result is still in L2 at kernel end
 }
 
 
@@ -475,7 +475,9 @@ def main():
                     help="batch sizes of the decode measurement, e.g. 1,16")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"gemv": 1000, "prefill": 300}[args.workload] if args.impl == "b200" else 10
+        # prefill: 100 steps = 36 ms of back-to-back GEMMs, the regime the burst peak is measured in (at 115 ms
+        # the same kernel is 6 % slower, at 0.4 s 10 % with sw_power_cap active and the SM clock at 1740 MHz)
+        args.steps = {"gemv": 1000, "prefill": 100}[args.workload] if args.impl == "b200" else 10
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
