@@ -25,9 +25,11 @@
 //               K=16) four times per K block and half, A and B from shared-memory descriptors,
 //               fp32 accumulators in TMEM (all 512 columns: 256 per half); tcgen05.commit hands
 //               the A and B stages back and, after the last K block, publishes each half.
-//   warps 4-7   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, fp32 -> fp16 (RN), 16-byte
-//               global stores into row-major y.  The halves are drained in order and handed back
-//               one by one, so the next tile's MMAs on half 0 start while half 1 is still drained.
+//   warps 4-7, 24-27  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, fp32 -> fp16 (RN),
+//               16-byte global stores into row-major y; a warp reads the TMEM lane quadrant
+//               (warp & 3), warps 4-7 take columns 0..127 of a half and warps 24-27 columns 128..255.
+//               The halves are drained in order and handed back one by one, so the next tile's
+//               MMAs on half 0 start while half 1 is still drained.
 //
 // Out-of-range rows (M, N tails) and columns (K tail) are zero-filled by the TMA unit: a zero
 // scale makes the weight +-0, a zero x makes the product 0, the epilogue skips them.
@@ -59,7 +61,7 @@ constexpr int kRawBytes = BN * 64;            // 16384: 256 rows x 16 words
 constexpr int kScBytes = BN * 16;             // 4096:  256 rows x 8 scales
 constexpr int kDequantWarps = 8;          // per group; two groups take alternate K blocks
 constexpr int kDequantGroups = 2;
-constexpr int kNumThreads = 256 + kDequantGroups * kDequantWarps * 32;   // 768
+constexpr int kNumThreads = 256 + kDequantGroups * kDequantWarps * 32 + 128;   // 896: warps 24-27 are a second set of epilogue warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint64_t kWaitNs = 4000000000ull;   // 4 s
 
@@ -179,7 +181,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     for (int i = 0; i < SA; ++i) { mbar_init(&sm.a_full[i], 1); mbar_init(&sm.a_empty[i], 1); }
     for (int i = 0; i < SB; ++i) { mbar_init(&sm.b_full[i], kDequantWarps); mbar_init(&sm.b_empty[i], 1); }
     for (int i = 0; i < SR; ++i) { mbar_init(&sm.raw_full[i], 1); mbar_init(&sm.raw_empty[i], kDequantGroups * kDequantWarps); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 8); }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -281,9 +283,10 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         if (nhalf == 1) umma_commit(&sm.acc_full[1]);
       }
     }
-  } else if (warp >= 4 && warp < 8) {
+  } else if ((warp >= 4 && warp < 8) || warp >= 24) {
     // ------------------------------------------------------------------ epilogue
-    const int ew = warp - 4;                       // TMEM lane quadrant this warp may read
+    const int ew = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int chalf = warp >= 24 ? 1 : 0;          // which 128 columns of each half this warp drains
     uint32_t it_tile = 0;
     const bool vec_ok = (p.N % 8) == 0;
     Work w;
@@ -296,10 +299,10 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)h * BN;
         if (h < w.nhalf && w.tok0 + h * BM < p.M) {  // (warp-uniform) half computed and holds real tokens
           uint32_t v[32];
-          tmem_ld_32x32b_x32(taddr, v);
+          tmem_ld_32x32b_x32(taddr + chalf * 128, v);
           tmem_ld_wait();
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
+          for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
             // pack this chunk, start the next chunk's TMEM load, then store: the load's latency
             // overlaps the stores
             uint4 o[4];
@@ -310,7 +313,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
               o[q].z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])));
               o[q].w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
             }
-            if (c + 1 < BN / 32) tmem_ld_32x32b_x32(taddr + (c + 1) * 32, v);
+            if (c + 1 < chalf * 4 + 4) tmem_ld_32x32b_x32(taddr + (c + 1) * 32, v);
             const int col0 = tn * BN + c * 32;
             if (row < p.M && col0 < p.N) {
               __half* dst = p.y + (int64_t)row * p.N + col0;
