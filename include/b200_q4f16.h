@@ -115,7 +115,10 @@ B200_API int b200_q4f16_gemm_ws(const void* x, const void* wq, const void* scale
  * copies asynchronous): copies x to `x_dev`, runs the kernel, copies `y_dev` back to y_host,
  * all on `cuda_stream`.  x_dev / y_dev are caller-owned device staging buffers of M*K and M*N
  * fp16.  The weights stay on the device, as parameters do in the reference's VM
- * (python/tvm/relax/vm.py:620-629). */
+ * (python/tvm/relax/vm.py:620-629).  Transfers of up to 256 KB from or to page-locked host
+ * buffers (16-byte aligned) are done by small kernels through the buffer's device mapping instead
+ * of the copy engine, the result copy as a programmatic dependent of the matmul; pageable
+ * buffers and larger transfers use cudaMemcpyAsync.  Either way the call returns after enqueueing. */
 B200_API int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, const void* scales, void* y_dev,
                            void* y_host, int64_t M, int64_t N, int64_t K, void* cuda_stream);
 
