@@ -124,6 +124,7 @@ rope_kv_append_kernel(const __half* __restrict__ qkv, const float* __restrict__ 
 // [split*chunk, min(ctx, (split+1)*chunk)) with an online softmax in fp32 and writes the partial
 // (max, sum, acc[128]) to scratch [B, nh, nsplit, 130] floats.  4 warps; lane owns 4 of the 128 dims.
 constexpr int kAttnChunk = 128;
+template <int kTok>
 __global__ void __launch_bounds__(128)
 attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
                            const __half* __restrict__ v_cache, const int* __restrict__ pos_ptr,
@@ -147,9 +148,10 @@ attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restric
   const int64_t tok_stride = (int64_t)nh * 128;
   const __half* kb = k_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
   const __half* vb = v_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
-  // Eight tokens per round: all sixteen loads are issued before the first use (a single query has
+  // kTok tokens per round: all 2*kTok loads are issued before the first use (a single query has
   // no other parallelism to cover the memory latency), then one online-softmax update per round.
-  constexpr int kTok = 8;
+  // 16 tokens (two rounds per warp and chunk) when the grid is small and latency decides, 8 when
+  // the batch fills the GPU and the kernel streams at the HBM rate anyway.
   for (int tb = t0 + warp * kTok; tb < t1; tb += 4 * kTok) {
     uint2 kv[kTok], vv[kTok];
 #pragma unroll
@@ -533,7 +535,11 @@ int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, co
   const int nsplit = (int)((max_ctx + kAttnChunk - 1) / kAttnChunk);
   auto s = static_cast<cudaStream_t>(stream);
   const float scale_log2e = 1.4426950408889634f / sqrtf(128.f);
-  rc = launch("attn_decode_partial", attn_decode_partial_kernel, dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B),
+  // few CTAs (small batch): latency bound, more loads in flight per warp (measured: 7B shape, context
+  // 2048, batch 1: -2 us per layer; batch 16: no gain, so the 8-token form stays there)
+  const bool small_grid = (int64_t)nsplit * nh * B < 2048;
+  rc = launch("attn_decode_partial", small_grid ? attn_decode_partial_kernel<16> : attn_decode_partial_kernel<8>,
+              dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B),
               dim3(128), 0, s, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, (const int*)pos,
               (float*)scratch, (int)nh, (int)max_ctx, nsplit, scale_log2e);
   if (rc) return rc;

@@ -397,7 +397,43 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   // CTA 0 also writes r out as the updated residual stream.
   __shared__ float s_part[16][CW];
   __shared__ float s_inv[16];
-  if (PRO == kPrologueRmsNorm) {
+  // One activation row of at most 2 * 8 * kConsumers values: a thread's two 8-value words are the
+  // same in the statistics pass and in the staging pass, so x, delta and the norm weight are loaded
+  // once, all six loads in flight together, and kept in registers across the two barriers.
+  const bool rms_one_pass = PRO == kPrologueRmsNorm && NC == 1 && nkb == 1 && p.K <= kConsumers * 16;
+  uint4 rms_keep[2], rms_w[2];
+  if (PRO == kPrologueRmsNorm && rms_one_pass) {
+    uint4 d[2];
+    bool live[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int k = (tid + r * kConsumers) * 8;
+      live[r] = k < p.K;
+      rms_keep[r] = d[r] = rms_w[r] = make_uint4(0, 0, 0, 0);
+      if (live[r]) {
+        rms_keep[r] = *reinterpret_cast<const uint4*>(p.x + k);
+        if (p.delta) d[r] = *reinterpret_cast<const uint4*>(p.delta + k);
+        rms_w[r] = *reinterpret_cast<const uint4*>(p.norm_w + k);
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (!live[r]) continue;
+      const int k = (tid + r * kConsumers) * 8;
+      if (p.delta) rms_keep[r] = add_f16x8(rms_keep[r], d[r]);
+      if (p.x_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(p.x_out + k) = rms_keep[r];
+      const __half2* h = reinterpret_cast<const __half2*>(&rms_keep[r]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) s_part[0][warp] = ss;
+  } else if (PRO == kPrologueRmsNorm) {
     // four rows at a time so that eight independent loads are in flight per thread
     constexpr int R = NC >= 8 ? 4 : 1;
     for (int m0 = 0; m0 < p.M; m0 += R) {
@@ -432,6 +468,8 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         if (lane == 0 && m0 + r < p.M) s_part[m0 + r][warp] = ss[r];
       }
     }
+  }
+  if (PRO == kPrologueRmsNorm) {
     bar_sync(1, kConsumers);
     if (tid < p.M) {
       float tot = 0.f;
@@ -442,12 +480,30 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     bar_sync(1, kConsumers);
   }
 
+  // (one K block in this case: the staged row is complete before the loop, the kept registers end here)
+  if (PRO == kPrologueRmsNorm && rms_one_pass) {
+    const int words = p.kblk >> 3;
+    const float inv = s_inv[0];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int j = tid + r * kConsumers;
+      if (j >= words) continue;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j * 8 < p.K) v = scale_f16x8(rms_keep[r], inv, rms_w[r]);
+      uint4 q;
+      q.x = __byte_perm(v.x, v.z, 0x5410);
+      q.y = __byte_perm(v.x, v.z, 0x7632);
+      q.z = __byte_perm(v.y, v.w, 0x5410);
+      q.w = __byte_perm(v.y, v.w, 0x7632);
+      xs[XLayout<NC>::slot(j, 0)] = q;
+    }
+  }
   for (int kb = 0; kb < nkb; ++kb) {
     const int k_lo = kb * p.kblk;
     const int k_hi = min(p.K, k_lo + p.kblk);
     // ---- stage x[:, k_lo .. k_lo + kblk) permuted per 8 k; zero beyond K and beyond M --------------
     if (kb > 0) bar_sync(1, kConsumers);         // everyone is done reading the previous block
-    {
+    if (!(PRO == kPrologueRmsNorm && rms_one_pass)) {
       // four items per thread and round: all loads of a round are issued before the first use
       const int words = p.kblk >> 3;
       const int items = words * NC;
