@@ -155,7 +155,9 @@ def oracle_steps(cfg, layers, embed, final_norm, lm_head, tokens, steps, max_ctx
     return out
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (3, 300, 4096), (16, 64, 256), (8, 4096, 2816)])
+# M = 1 with K <= 4096 takes the one-pass form of the RMSNorm prologue (row kept in registers)
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (1, 4096, 4096), (1, 272, 2304), (1, 128, 8192), (3, 300, 4096), (16, 64, 256),
+                                   (8, 4096, 2816)])
 def test_gemv_with_fused_neighbours(cuda_lib, M, N, K):
     from relax_b200 import synth
     from util import assert_matmul_close
