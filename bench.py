@@ -316,6 +316,21 @@ def run_gpu(args):
     L = _lib.lib()
     peaks = measured_peaks()
 
+    if args.decode_only:
+        decode = [run_decode(args, world, rank, dev, b) for b in args.decode_batches]
+        if rank == 0:
+            d0 = decode[0]
+            print(json.dumps({"metric": d0["metric"], "value": d0["value"], "unit": d0["unit"], "n_gpus": world,
+                              "steps": d0["steps"], "warmup": 3, "ms_per_step": d0["ms_per_token_step"],
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                              "dtype": "f16 (int4 weights, fp32 accumulate)", "data": "synthetic",
+                              "config": {"workload": f"7B-shaped decode, batch {d0['batch']}, context {d0['context']}, tp {world}"},
+                              "e2e": d0["e2e"], "gpu_launches": d0["kernels_per_step"] * d0["steps"], "decode": decode}),
+                  flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
     if args.workload == "gemv":
         m, n, k = 1, 4096, 4096
         copies = args.copies
@@ -468,6 +483,8 @@ def main():
     ap.add_argument("--shape", default=None, help="M,N,K override (profiling of other shapes of the same kernels)")
     ap.add_argument("--no-graph", action="store_true", help="launch directly instead of replaying a CUDA graph")
     ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shaped decode measurement")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="only the 7B-shaped decode measurement, as the line's own metric (for profiling the decode step)")
     ap.add_argument("--decode-attn1", action="store_true", help="rotary + attention + merge as one launch (measured slightly slower in a graph)")
     ap.add_argument("--decode-nccl", action="store_true", help="tensor-parallel sums through NCCL instead of the fused kernel")
     ap.add_argument("--decode-steps", type=int, default=32, help="timed tokens per sequence of the decode measurement")
