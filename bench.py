@@ -221,7 +221,7 @@ def run_decode(args, world, rank, dev, batch):
     lm_head = embed[rank * vl:(rank + 1) * vl].contiguous()      # tied fp16 head, vocabulary-sharded
     final_norm = torch.ones(cfg.hidden, dtype=torch.float16, device=dev)
     eng = decoder.DecodeEngine(cfg, layers, embed, final_norm, lm_head, batch, max_ctx, dev, rank, world,
-                               peer_reduce=not args.decode_nccl, fused_attention=args.decode_attn1)
+                               peer_reduce=not args.decode_nccl, fused_attention="rope" if args.decode_attn2 else args.decode_attn1)
     for kc, vc in zip(eng.kc, eng.vc):                            # a full context of N(0,1) keys and values
         kc.normal_(generator=gen)
         vc.normal_(generator=gen)
@@ -486,6 +486,7 @@ def main():
     ap.add_argument("--decode-only", action="store_true",
                     help="only the 7B-shaped decode measurement, as the line's own metric (for profiling the decode step)")
     ap.add_argument("--decode-attn1", action="store_true", help="rotary + attention + merge as one launch (measured slightly slower in a graph)")
+    ap.add_argument("--decode-attn2", action="store_true", help="rotary + KV append inside the attention launch, merge as a second launch")
     ap.add_argument("--decode-nccl", action="store_true", help="tensor-parallel sums through NCCL instead of the fused kernel")
     ap.add_argument("--decode-steps", type=int, default=32, help="timed tokens per sequence of the decode measurement")
     ap.add_argument("--decode-batches", type=lambda v: [int(x) for x in v.split(",")], default=[1],

@@ -224,6 +224,13 @@ B200_API int b200_attn_decode_fused(const void* qkv, const void* cos_t, const vo
                                     void* v_cache, void* out, void* scratch, int64_t B, int64_t nh, int64_t max_ctx,
                                     void* cuda_stream);
 
+/* The same in two launches: rotary embedding, KV append and the per-chunk attention in the first, the
+ * merge of the partials in the second (no arrival counters).  Arguments as b200_attn_decode_fused;
+ * `scratch` needs b200_attn_decode_scratch_bytes(B, nh, max_ctx) bytes and no initialisation. */
+B200_API int b200_attn_decode_rope(const void* qkv, const void* cos_t, const void* sin_t, const void* pos, void* k_cache,
+                                   void* v_cache, void* out, void* scratch, int64_t B, int64_t nh, int64_t max_ctx,
+                                   void* cuda_stream);
+
 /* Same attention for callers that cannot hand over scratch memory.  (No counterpart in the
  * reference.)  Some hosts of this library are not allowed to allocate device memory at the point
  * where they call it: a runtime whose memory planner has already fixed every buffer of the step,

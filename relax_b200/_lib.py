@@ -82,6 +82,7 @@ PROTOTYPES = {
     "b200_attn_decode": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_fused_scratch_bytes": (_i64, [_i64, _i64, _i64]),
     "b200_attn_decode_fused": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_attn_decode_rope": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_static": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_silu_mul": (_ci, [_vp, _vp, _i64, _i64, _vp]),
     "b200_embed_rows": (_ci, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),

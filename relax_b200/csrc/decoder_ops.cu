@@ -221,11 +221,12 @@ attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restric
 //   * bumps a per-(b, h) counter; the CTA that arrives last merges all chunks' partials and stores
 //     fp16.  The counters live after the partials in `scratch`, must be zero before the first call
 //     and are left zero.
+template <int kTok>
 __global__ void __launch_bounds__(128)
 attn_decode_fused_kernel(const __half* __restrict__ qkv, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                          const int* __restrict__ pos_ptr, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                          __half* __restrict__ out, float* __restrict__ scratch, int nh, int max_ctx, int nsplit,
-                         float scale_log2e) {
+                         float scale_log2e, int merge) {
   ptx::pdl_wait();
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int pos = pos_ptr[0];
@@ -282,7 +283,6 @@ attn_decode_fused_kernel(const __half* __restrict__ qkv, const float* __restrict
   const int64_t tok_stride = (int64_t)nh * 128;
   const __half* kb = k_cache + ((int64_t)b * max_ctx * nh + h) * 128 + d0;
   const __half* vb = v_cache + ((int64_t)b * max_ctx * nh + h) * 128 + d0;
-  constexpr int kTok = 8;
   for (int tb = t0 + warp * kTok; tb < t1; tb += 4 * kTok) {
     uint2 kv[kTok], vv[kTok];
 #pragma unroll
@@ -343,6 +343,7 @@ attn_decode_fused_kernel(const __half* __restrict__ qkv, const float* __restrict
     part[2 + d] = A;
     if (d == 0) { part[0] = M; part[1] = L; }
   }
+  if (!merge) return;                              // the merge kernel follows as its own launch
   // ---- the CTA that arrives last for this (b, h) merges the chunks ---------------------------------
   __threadfence();
   __syncthreads();
@@ -392,13 +393,34 @@ attn_decode_combine_kernel(const float* __restrict__ scratch, const int* __restr
   const int ctx = pos_ptr[0] + 1;
   const int used = (ctx + kAttnChunk - 1) / kAttnChunk;
   const float* p = scratch + ((int64_t)b * nh + h) * nsplit * 130;
-  float M = -INFINITY;
-  for (int s = 0; s < used; ++s) M = fmaxf(M, p[s * 130]);
-  float L = 0.f, A = 0.f;
-  for (int s = 0; s < used; ++s) {
-    const float f = exp2f(p[s * 130] - M);
-    L += p[s * 130 + 1] * f;
-    A += p[s * 130 + 2 + d] * f;
+  // sixteen chunks per round, all 48 loads of a round issued together (the partials sit in L2), one
+  // online-softmax update per round
+  float M = -INFINITY, L = 0.f, A = 0.f;
+  for (int s0 = 0; s0 < used; s0 += 16) {
+    float Ms[16], Ls[16], As[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int si = min(s0 + j, used - 1);
+      Ms[j] = p[si * 130];
+      Ls[j] = p[si * 130 + 1];
+      As[j] = p[si * 130 + 2 + d];
+    }
+    float Mn = M;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (s0 + j < used) Mn = fmaxf(Mn, Ms[j]);
+    const float corr = exp2f(M - Mn);            // first round: exp2f(-inf) = 0
+    L *= corr;
+    A *= corr;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (s0 + j < used) {
+        const float f = exp2f(Ms[j] - Mn);
+        L += Ls[j] * f;
+        A += As[j] * f;
+      }
+    }
+    M = Mn;
   }
   ptx::pdl_launch_dependents();
   out[((int64_t)b * nh + h) * 128 + d] = __float2half_rn(A / L);
@@ -520,10 +542,30 @@ int b200_attn_decode_fused(const void* qkv, const void* cos_t, const void* sin_t
   if (rc) return rc;
   const int nsplit = (int)((max_ctx + kAttnChunk - 1) / kAttnChunk);
   const float scale_log2e = 1.4426950408889634f / sqrtf(128.f);
-  return launch("attn_decode_fused", attn_decode_fused_kernel, dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B), dim3(128), 0,
+  return launch("attn_decode_fused", attn_decode_fused_kernel<8>, dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B), dim3(128), 0,
                 static_cast<cudaStream_t>(stream), (const __half*)qkv, (const float*)cos_t, (const float*)sin_t,
                 (const int*)pos, (__half*)k_cache, (__half*)v_cache, (__half*)out, (float*)scratch, (int)nh, (int)max_ctx,
-                nsplit, scale_log2e);
+                nsplit, scale_log2e, 1);
+}
+
+int b200_attn_decode_rope(const void* qkv, const void* cos_t, const void* sin_t, const void* pos, void* k_cache, void* v_cache,
+                          void* out, void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* stream) {
+  if (B <= 0 || nh <= 0 || max_ctx <= 0 || B > 65535 || nh > 65535) return fail(B200_EINVAL, "attn_decode_rope: bad sizes");
+  if (!qkv || !cos_t || !sin_t || !pos || !k_cache || !v_cache || !out || !scratch)
+    return fail(B200_EINVAL, "attn_decode_rope: null pointer");
+  int rc = ensure_device();
+  if (rc) return rc;
+  const int nsplit = (int)((max_ctx + kAttnChunk - 1) / kAttnChunk);
+  const float scale_log2e = 1.4426950408889634f / sqrtf(128.f);
+  auto s = static_cast<cudaStream_t>(stream);
+  const bool small_grid = (int64_t)nsplit * nh * B < 2048;
+  rc = launch("attn_decode_rope", small_grid ? attn_decode_fused_kernel<16> : attn_decode_fused_kernel<8>,
+              dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B), dim3(128), 0, s, (const __half*)qkv, (const float*)cos_t,
+              (const float*)sin_t, (const int*)pos, (__half*)k_cache, (__half*)v_cache, (__half*)out, (float*)scratch, (int)nh,
+              (int)max_ctx, nsplit, scale_log2e, 0);
+  if (rc) return rc;
+  return launch("attn_decode_combine", attn_decode_combine_kernel, dim3((unsigned)nh, (unsigned)B), dim3(128), 0, s,
+                (const float*)scratch, (const int*)pos, (__half*)out, (int)nh, nsplit);
 }
 
 int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out, void* scratch,

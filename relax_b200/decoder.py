@@ -102,7 +102,7 @@ class DecodeEngine:
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
                  device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True,
-                 fused_attention: bool = False):
+                 fused_attention=False):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
@@ -117,7 +117,9 @@ class DecodeEngine:
         # fused: RMSNorm (+ residual add) and SwiGLU run inside the staging of the next skinny matmul
         # (7 kernels per layer instead of 11); needs batch <= 16, the skinny kernel's range
         self.fused = bool(fused) and B <= 16
-        self.fused_attention = bool(fused_attention)
+        # False: rotary/append, attention, merge as three launches; True: one launch; "rope": rotary/append
+        # inside the attention launch, merge as a second launch
+        self.fused_attention = "rope" if fused_attention == "rope" else bool(fused_attention)
         self.x = torch.zeros((B, H), **f16)            # residual stream
         self.x2 = torch.zeros((B, H), **f16)           # its second buffer (fused path ping-pongs)
         self.h = torch.zeros((B, H), **f16)            # normalised activations
@@ -208,7 +210,12 @@ class DecodeEngine:
         else:
             self._check(L.b200_rmsnorm(self.x.data_ptr(), dptr, w["norm1"].data_ptr(), self.h.data_ptr(), B, H, cfg.eps, sp))
             self._matmul(self.h, w["qkv"], self.qkv, 3 * hl, H, sp)
-        if self.fused_attention:
+        if self.fused_attention == "rope":
+            # rotary embedding + KV append + per-chunk attention in one launch, the merge in a second
+            self._check(L.b200_attn_decode_rope(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
+                                                self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.attn.data_ptr(),
+                                                self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
+        elif self.fused_attention:
             # rotary embedding + KV append + attention + merge in one launch
             self._check(L.b200_attn_decode_fused(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
                                                  self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.attn.data_ptr(),
@@ -276,7 +283,7 @@ class DecodeEngine:
 
     def kernels_per_step(self) -> int:
         """Kernels of this library launched by one step (embed + 5 or 11 per layer + final norm + advance)."""
-        return 1 + len(self.layers) * ((5 if self.fused else 9) + (0 if self.fused_attention else 2)) + 1 + 2
+        return 1 + len(self.layers) * ((5 if self.fused else 9) + (1 if self.fused_attention == "rope" else (0 if self.fused_attention else 2))) + 1 + 2
 
     def capture(self, stream):
         """Captures one step into a CUDA graph on `stream` (after one eager warm-up step, which

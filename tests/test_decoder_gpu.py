@@ -114,6 +114,16 @@ def test_rope_append_attention(cuda_lib, B, nh, ctx, max_ctx):
         assert (tv2.cpu().numpy().view(np.uint16) == tv.cpu().numpy().view(np.uint16)).all()
         close(out2.cpu().numpy(), ref, 4e-3, 2e-3, "fused attention")
     assert int(fscratch[-B * nh:].view(torch.int32).abs().sum().item()) == 0, "arrival counters are left at zero"
+    # the two-launch form: rotary + append + per-chunk attention, then the merge (no counters, scratch not initialised)
+    tk3, tv3 = dev(kc0), dev(vc0)
+    out3 = torch.empty((B, nh * D), dtype=torch.float16, device="cuda")
+    rscratch = torch.full((nbytes // 4,), float("nan"), dtype=torch.float32, device="cuda")
+    assert cuda_lib.b200_attn_decode_rope(tq.data_ptr(), tcos.data_ptr(), tsin.data_ptr(), tpos.data_ptr(), tk3.data_ptr(),
+                                          tv3.data_ptr(), out3.data_ptr(), rscratch.data_ptr(), B, nh, max_ctx, 0) == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    close(tk3.cpu().numpy()[:, pos], k, 2e-3, 2e-3, "rotated k appended by the two-launch form")
+    assert (tv3.cpu().numpy().view(np.uint16) == tv.cpu().numpy().view(np.uint16)).all()
+    close(out3.cpu().numpy(), ref, 4e-3, 2e-3, "two-launch attention")
 
 
 def test_embed_and_advance(cuda_lib):
