@@ -209,7 +209,11 @@ B200_API int b200_rope_kv_append(const void* qkv, const void* cos_t, const void*
 
 /* out fp16 [B, nh*128] = softmax(q.K^T / sqrt(128)) . V over positions 0..*pos.  `scratch` is
  * caller-owned device memory of b200_attn_decode_scratch_bytes(B, nh, max_ctx) bytes holding the
- * per-chunk partial results (two launches: partials over 128-token chunks, then the merge). */
+ * per-chunk partial results (two launches: partials over 128-token chunks, then the merge). 
+ * Ordering: *pos and the cache entries at positions below *pos are read BEFORE the kernel synchronises with
+ * the launch in front of it in the stream (its first K/V loads overlap that kernel's tail), so they must
+ * not be written by the launch immediately before this call; the entry at *pos itself and q may be (that
+ * is what b200_rope_kv_append does). */
 B200_API int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t max_ctx);
 B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
                               void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);

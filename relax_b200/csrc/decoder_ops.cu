@@ -129,7 +129,9 @@ __global__ void __launch_bounds__(128)
 attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
                            const __half* __restrict__ v_cache, const int* __restrict__ pos_ptr,
                            float* __restrict__ scratch, int nh, int max_ctx, int nsplit, float scale_log2e) {
-  ptx::pdl_wait();
+  // Everything up to the wait reads only what kernels at least two launches back have written (the
+  // position, and cache entries older than the new token): the first round of K/V loads of a chunk
+  // that does not hold the new token is in flight while the kernel before this one finishes.
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int ctx = pos_ptr[0] + 1;
   const int t0 = split * kAttnChunk;
@@ -137,6 +139,23 @@ attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restric
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* out = scratch + (((int64_t)b * nh + h) * nsplit + split) * 130;
   __shared__ float sm_m[4], sm_l[4], sm_acc[4][128];
+  const int64_t tok_stride = (int64_t)nh * 128;
+  const __half* kb = k_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
+  const __half* vb = v_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
+  uint2 kv[kTok], vv[kTok];
+  auto load_round = [&](int tb) {
+#pragma unroll
+    for (int j = 0; j < kTok; ++j) {
+      const int t = min(tb + j, t1 - 1);             // clamped: a token past the end is loaded but not used
+      kv[j] = *reinterpret_cast<const uint2*>(kb + t * tok_stride);
+      vv[j] = *reinterpret_cast<const uint2*>(vb + t * tok_stride);
+    }
+  };
+  int tb = t0 + warp * kTok;
+  const bool early = t1 < ctx;                       // the new token (position ctx - 1) is not in this chunk
+  if (early && tb < t1) load_round(tb);
+  ptx::pdl_wait();
+  if (!early && tb < t1) load_round(tb);
   float qf[4];
   {
     uint2 qv = *reinterpret_cast<const uint2*>(q + ((int64_t)b * nh + h) * 128 + lane * 4);
@@ -145,21 +164,12 @@ attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restric
     qf[0] = a.x * scale_log2e; qf[1] = a.y * scale_log2e; qf[2] = c.x * scale_log2e; qf[3] = c.y * scale_log2e;
   }
   float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const int64_t tok_stride = (int64_t)nh * 128;
-  const __half* kb = k_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
-  const __half* vb = v_cache + ((int64_t)b * max_ctx * nh + h) * 128 + lane * 4;
   // kTok tokens per round: all 2*kTok loads are issued before the first use (a single query has
   // no other parallelism to cover the memory latency), then one online-softmax update per round.
   // 16 tokens (two rounds per warp and chunk) when the grid is small and latency decides, 8 when
   // the batch fills the GPU and the kernel streams at the HBM rate anyway.
-  for (int tb = t0 + warp * kTok; tb < t1; tb += 4 * kTok) {
-    uint2 kv[kTok], vv[kTok];
-#pragma unroll
-    for (int j = 0; j < kTok; ++j) {
-      const int t = min(tb + j, t1 - 1);             // clamped: a token past the end is loaded but not used
-      kv[j] = *reinterpret_cast<const uint2*>(kb + t * tok_stride);
-      vv[j] = *reinterpret_cast<const uint2*>(vb + t * tok_stride);
-    }
+  for (; tb < t1; tb += 4 * kTok) {
+    if (tb != t0 + warp * kTok) load_round(tb);      // (the first round is already in flight)
     float s[kTok];
 #pragma unroll
     for (int j = 0; j < kTok; ++j) {
