@@ -131,6 +131,14 @@ B200_API int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void*
 B200_API int b200_q4f16_matmul_dl(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales,
                          B200DLTensor* y);
 B200_API int b200_q4f16_dequantize_dl(const B200DLTensor* wq, const B200DLTensor* scales, B200DLTensor* w_out);
+/* b200_q4f16_matmul_dl with the kernel family chosen by the caller instead of by M: what the BYOC
+ * codegen's option {"family": ...} selects (options reach a codegen through RunCodegen's map,
+ * src/relax/transform/run_codegen.cc:42,155).  B200_FAMILY_GEMV requires 1 <= M <= 16. */
+#define B200_FAMILY_AUTO 0
+#define B200_FAMILY_GEMV 1
+#define B200_FAMILY_GEMM 2
+B200_API int b200_q4f16_matmul_dl_family(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales,
+                                         B200DLTensor* y, int32_t family);
 
 /* ---- packed-function symbols of the reference's C backend ABI ---------------------------
  * Signature TVMBackendPackedCFunc (include/tvm/runtime/c_backend_api.h:49-51); the form the
@@ -175,7 +183,9 @@ B200_API int b200_q4f16_gemv_swiglu(const void* gu, const void* wq, const void* 
  * has completed in between (two alternating call sites, as o-proj and down-proj of a decoder layer,
  * satisfy this).  1 <= M <= 16, K % 256 == 0, N % 8 == 0, scales 16-byte aligned, world <= 8.
  * swiglu != 0: x is gate|up [M,2K] and silu(gate)*up is applied first (see b200_q4f16_gemv_swiglu).
- * A wait that runs out sets bit 4 of the skinny kernel's byte in b200_device_error_flags(). */
+ * A wait that runs out (after option "gemv.peer_wait_ms", default 2000) sets bit 4 of the skinny kernel's
+ * byte in b200_device_error_flags(); the kernel still finishes and writes `out` from whatever the peers'
+ * buffers hold. */
 typedef struct {
   int32_t world, rank;
   const void* peer_y[8];
@@ -209,14 +219,28 @@ B200_API int b200_rope_kv_append(const void* qkv, const void* cos_t, const void*
 
 /* out fp16 [B, nh*128] = softmax(q.K^T / sqrt(128)) . V over positions 0..*pos.  `scratch` is
  * caller-owned device memory of b200_attn_decode_scratch_bytes(B, nh, max_ctx) bytes holding the
- * per-chunk partial results (two launches: partials over 128-token chunks, then the merge). 
- * Ordering: *pos and the cache entries at positions below *pos are read BEFORE the kernel synchronises with
- * the launch in front of it in the stream (its first K/V loads overlap that kernel's tail), so they must
- * not be written by the launch immediately before this call; the entry at *pos itself and q may be (that
- * is what b200_rope_kv_append does). */
+ * per-chunk partial results (two launches: partials over 128-token chunks, then the merge).
+ * B, nh <= 65535.
+ *
+ * flags = 0: every input is read after the kernel has synchronised with the launch in front of it in
+ * the stream; any sequence of launches is safe.
+ * flags = B200_ATTN_EARLY_KV_LOADS: *pos and the cache entries at positions BELOW *pos are read before
+ * that synchronisation, so that the first K/V loads overlap the tail of the preceding kernel.  The
+ * attention kernel may then start while the kernel TWO launches back is still running, unless the
+ * launch directly in front of it waits for its own predecessor before it lets its dependents start.
+ * So set the flag only when both hold:
+ *   (1) the launch directly in front of this call writes neither *pos nor a cache entry below *pos, and
+ *       it is either not a programmatic-dependent launch or one that executes griddepcontrol.wait before
+ *       griddepcontrol.launch_dependents (b200_rope_kv_append, b200_rmsnorm, b200_silu_mul,
+ *       b200_embed_rows and b200_advance_pos of this library do; the q4f16 matmul entry points do NOT:
+ *       they release their dependents first, so with one of them directly in front, leave the flag clear);
+ *   (2) whatever last wrote *pos or those cache entries was launched before that launch.
+ * The entry at *pos itself and q may be written by the launch directly in front (that is what
+ * b200_rope_kv_append does; the decode engine of this repository calls it there and sets the flag). */
+#define B200_ATTN_EARLY_KV_LOADS 1u
 B200_API int64_t b200_attn_decode_scratch_bytes(int64_t B, int64_t nh, int64_t max_ctx);
 B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
-                              void* scratch, int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);
+                              void* scratch, int64_t B, int64_t nh, int64_t max_ctx, uint32_t flags, void* cuda_stream);
 
 /* Rotary embedding of q and k, KV append at *pos, attention over positions 0..*pos and the merge of
  * the per-chunk partials in one launch (what b200_rope_kv_append + b200_attn_decode do in three).
@@ -247,9 +271,10 @@ B200_API int b200_attn_decode_rope(const void* qkv, const void* cos_t, const voi
  *     do this first call outside any stream capture).
  *   - All calls on a device share the one array: two calls that overlap on the GPU (different
  *     streams) overwrite each other's partial results.  Calls ordered on one stream are safe; every
- *     slot that is read has been written by the same call, so nothing needs clearing in between. */
+ *     slot that is read has been written by the same call, so nothing needs clearing in between.
+ *   - `flags` as for b200_attn_decode (0 is always safe). */
 B200_API int b200_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
-                                     int64_t B, int64_t nh, int64_t max_ctx, void* cuda_stream);
+                                     int64_t B, int64_t nh, int64_t max_ctx, uint32_t flags, void* cuda_stream);
 
 /* out[b,:] = table[ids[b],:]: fp16 table [vocab,H], int32 ids [B] on the device (ids are clamped
  * to the table).  H % 8 == 0.  (reference: relax.take, python/tvm/relax/transform/legalize_ops.py:168) */
@@ -273,7 +298,7 @@ B200_API void b200_reset_launch_count(void);
  * Returns the flag bits (>= 0) or a negative B200_E* code. */
 B200_API int b200_device_error_flags(void);
 
-/* Selects a kernel variant / tuning knob by name (e.g. "gemv.warps"); returns B200_EINVAL for
+/* Selects a kernel variant / tuning knob by name (e.g. "gemv.warps", "gemv.peer_wait_ms"); returns B200_EINVAL for
  * an unknown name or value.  Intended for benchmarking sweeps; defaults are the tuned ones. */
 B200_API int b200_set_option(const char* name, int64_t value);
 B200_API int64_t b200_get_option(const char* name);

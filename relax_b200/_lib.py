@@ -12,6 +12,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("B200_Q4F16_LIB") or os.path.join(_HERE, "libb200_q4f16.so")
 
 OK, EINVAL, ENODEVICE, ELAUNCH, EDEVICE, ENOTREADY = 0, -1, -2, -3, -4, -5
+ATTN_EARLY_KV_LOADS = 1   # B200_ATTN_EARLY_KV_LOADS
+FAMILY_AUTO, FAMILY_GEMV, FAMILY_GEMM = 0, 1, 2
 
 
 class B200Error(RuntimeError):
@@ -71,6 +73,7 @@ PROTOTYPES = {
     "b200_q4f16_matmul_host": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_matmul_dl": (_ci, [_dlp, _dlp, _dlp, _dlp]),
     "b200_q4f16_dequantize_dl": (_ci, [_dlp, _dlp, _dlp]),
+    "b200_q4f16_matmul_dl_family": (_ci, [_dlp, _dlp, _dlp, _dlp, ctypes.c_int32]),
     "b200_q4f16_matmul_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_dequantize_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_gemv_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
@@ -79,11 +82,11 @@ PROTOTYPES = {
     "b200_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _vp]),
     "b200_rope_kv_append": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_scratch_bytes": (_i64, [_i64, _i64, _i64]),
-    "b200_attn_decode": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_attn_decode": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_uint32, _vp]),
     "b200_attn_decode_fused_scratch_bytes": (_i64, [_i64, _i64, _i64]),
     "b200_attn_decode_fused": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_rope": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
-    "b200_attn_decode_static": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_attn_decode_static": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_uint32, _vp]),
     "b200_silu_mul": (_ci, [_vp, _vp, _i64, _i64, _vp]),
     "b200_embed_rows": (_ci, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_advance_pos": (_ci, [_vp, _i64, _vp]),

@@ -231,7 +231,7 @@ int host_copy(const void* src, void* dst, size_t bytes, bool dependent, cudaStre
 extern "C" {
 
 const char* b200_last_error(void) { return g_err; }
-int b200_abi_version(void) { return 100; }
+int b200_abi_version(void) { return 101; }
 
 int b200_set_stream(void* s) {
   g_stream = static_cast<cudaStream_t>(s);
@@ -257,8 +257,7 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "gemv.stages")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.stages in 0..16"); o.gemv_stages = v; }
   else if (!strcmp(name, "gemv.pdl")) { o.gemv_pdl = v != 0; }
   else if (!strcmp(name, "gemv.ctas_per_sm")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemv.ctas_per_sm in 0..8"); o.gemv_ctas_per_sm = v; }
-  else if (!strcmp(name, "gemm.variant")) { if (v < 0 || v > 63) return fail(B200_EINVAL, "gemm.variant in 0..63"); o.gemm_variant = v; }
-  else if (!strcmp(name, "gemm.stages")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemm.stages in 0..8"); o.gemm_stages = v; }
+  else if (!strcmp(name, "gemv.peer_wait_ms")) { if (v < 1 || v > 60000) return fail(B200_EINVAL, "gemv.peer_wait_ms in 1..60000"); o.gemv_peer_wait_ms = v; }
   else if (!strcmp(name, "gemm.ws_ksplit")) { if (v < 0 || v > 8 || (v & (v - 1))) return fail(B200_EINVAL, "gemm.ws_ksplit is 0, 1, 2, 4 or 8"); o.gemm_ws_ksplit = v; }
   else if (!strcmp(name, "gemm.ws_max_m")) { if (v < 0 || v > 128) return fail(B200_EINVAL, "gemm.ws_max_m in 0..128"); o.gemm_ws_max_m = v; }
   else if (!strcmp(name, "gemm.max_ctas")) { if (v < 0 || v > 1024) return fail(B200_EINVAL, "gemm.max_ctas in 0..1024"); o.gemm_max_ctas = v; }
@@ -274,8 +273,7 @@ int64_t b200_get_option(const char* name) {
   if (!strcmp(name, "gemv.stages")) return o.gemv_stages;
   if (!strcmp(name, "gemv.pdl")) return o.gemv_pdl;
   if (!strcmp(name, "gemv.ctas_per_sm")) return o.gemv_ctas_per_sm;
-  if (!strcmp(name, "gemm.variant")) return o.gemm_variant;
-  if (!strcmp(name, "gemm.stages")) return o.gemm_stages;
+  if (!strcmp(name, "gemv.peer_wait_ms")) return o.gemv_peer_wait_ms;
   if (!strcmp(name, "gemm.max_ctas")) return o.gemm_max_ctas;
   if (!strcmp(name, "gemm.ws_ksplit")) return o.gemm_ws_ksplit;
   if (!strcmp(name, "gemm.ws_max_m")) return o.gemm_ws_max_m;
@@ -413,8 +411,15 @@ int b200_q4f16_matmul_host(const void* x_host, void* x_dev, const void* wq, cons
 }
 
 int b200_q4f16_matmul_dl(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales, B200DLTensor* y) {
+  return b200_q4f16_matmul_dl_family(x, wq, scales, y, B200_FAMILY_AUTO);
+}
+
+int b200_q4f16_matmul_dl_family(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales, B200DLTensor* y,
+                                int32_t family) {
   const char* who = "b200.q4f16_matmul";
   int dev = -1, rc;
+  if (family != B200_FAMILY_AUTO && family != B200_FAMILY_GEMV && family != B200_FAMILY_GEMM)
+    return fail(B200_EINVAL, "%s: unknown kernel family %d (0 auto, 1 skinny, 2 tensor-core)", who, (int)family);
   if ((rc = check_tensor(who, "x", x, 2, 16, &dev))) return rc;
   if ((rc = check_tensor(who, "wq", wq, 1, 32, &dev))) return rc;
   if ((rc = check_tensor(who, "scales", scales, 2, 16, &dev))) return rc;
@@ -431,7 +436,8 @@ int b200_q4f16_matmul_dl(const B200DLTensor* x, const B200DLTensor* wq, const B2
     return fail(B200_EINVAL, "%s: y is [%lld,%lld], expected [%lld,%lld]", who, (long long)y->shape[0],
                 (long long)y->shape[1], (long long)M, (long long)N);
   if ((rc = check_current_device(who, dev))) return rc;
-  return matmul_impl(kAuto, who, data_ptr(x), data_ptr(wq), data_ptr(scales), data_ptr(y), M, N, K, g_stream);
+  const Family fam = family == B200_FAMILY_GEMV ? kGemv : family == B200_FAMILY_GEMM ? kGemm : kAuto;
+  return matmul_impl(fam, who, data_ptr(x), data_ptr(wq), data_ptr(scales), data_ptr(y), M, N, K, g_stream);
 }
 
 int b200_q4f16_dequantize_dl(const B200DLTensor* wq, const B200DLTensor* scales, B200DLTensor* w_out) {

@@ -128,10 +128,14 @@ template <int kTok>
 __global__ void __launch_bounds__(128)
 attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache,
                            const __half* __restrict__ v_cache, const int* __restrict__ pos_ptr,
-                           float* __restrict__ scratch, int nh, int max_ctx, int nsplit, float scale_log2e) {
-  // Everything up to the wait reads only what kernels at least two launches back have written (the
-  // position, and cache entries older than the new token): the first round of K/V loads of a chunk
+                           float* __restrict__ scratch, int nh, int max_ctx, int nsplit, float scale_log2e,
+                           int early_ok) {
+  // early_ok: the caller promises that the position and the cache entries older than the new token were
+  // complete before the launch in front of this one BEGAN (see B200_ATTN_EARLY_KV_LOADS).  Then
+  // everything up to the wait reads only finished data, and the first round of K/V loads of a chunk
   // that does not hold the new token is in flight while the kernel before this one finishes.
+  // Without the promise nothing is read before the wait.
+  if (!early_ok) ptx::pdl_wait();
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int ctx = pos_ptr[0] + 1;
   const int t0 = split * kAttnChunk;
@@ -152,9 +156,9 @@ attn_decode_partial_kernel(const __half* __restrict__ q, const __half* __restric
     }
   };
   int tb = t0 + warp * kTok;
-  const bool early = t1 < ctx;                       // the new token (position ctx - 1) is not in this chunk
+  const bool early = early_ok && t1 < ctx;           // the new token (position ctx - 1) is not in this chunk
   if (early && tb < t1) load_round(tb);
-  ptx::pdl_wait();
+  if (early_ok) ptx::pdl_wait();
   if (!early && tb < t1) load_round(tb);
   float qf[4];
   {
@@ -579,8 +583,11 @@ int b200_attn_decode_rope(const void* qkv, const void* cos_t, const void* sin_t,
 }
 
 int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out, void* scratch,
-                     int64_t B, int64_t nh, int64_t max_ctx, void* stream) {
+                     int64_t B, int64_t nh, int64_t max_ctx, uint32_t flags, void* stream) {
   if (B <= 0 || nh <= 0 || max_ctx <= 0) return fail(B200_EINVAL, "attn_decode: bad sizes");
+  if (B > 65535 || nh > 65535 || max_ctx > 0x3fffffffLL)
+    return fail(B200_EINVAL, "attn_decode: batch and heads are limited to 65535 (grid dimensions), max_ctx to 2^30");
+  if (flags & ~(uint32_t)B200_ATTN_EARLY_KV_LOADS) return fail(B200_EINVAL, "attn_decode: unknown flag bits %#x", flags);
   if (!q || !k_cache || !v_cache || !pos || !out || !scratch) return fail(B200_EINVAL, "attn_decode: null pointer");
   int rc = ensure_device();
   if (rc) return rc;
@@ -593,7 +600,7 @@ int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, co
   rc = launch("attn_decode_partial", small_grid ? attn_decode_partial_kernel<16> : attn_decode_partial_kernel<8>,
               dim3((unsigned)nsplit, (unsigned)nh, (unsigned)B),
               dim3(128), 0, s, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, (const int*)pos,
-              (float*)scratch, (int)nh, (int)max_ctx, nsplit, scale_log2e);
+              (float*)scratch, (int)nh, (int)max_ctx, nsplit, scale_log2e, (int)(flags & B200_ATTN_EARLY_KV_LOADS));
   if (rc) return rc;
   return launch("attn_decode_combine", attn_decode_combine_kernel, dim3((unsigned)nh, (unsigned)B), dim3(128), 0, s,
                 (const float*)scratch, (const int*)pos, (__half*)out, (int)nh, nsplit);
@@ -624,10 +631,13 @@ constexpr int64_t kStaticAttnSlots = 8192;                       // e.g. 16 sequ
 static __device__ __align__(256) float g_attn_static_scratch[kStaticAttnSlots * 130];   // 4.26 MB per GPU
 
 int b200_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out, int64_t B,
-                            int64_t nh, int64_t max_ctx, void* stream) {
+                            int64_t nh, int64_t max_ctx, uint32_t flags, void* stream) {
   if (B <= 0 || nh <= 0 || max_ctx <= 0) return fail(B200_EINVAL, "attn_decode_static: bad sizes");
+  if (B > 65535 || nh > 65535 || max_ctx > 0x3fffffffLL)
+    return fail(B200_EINVAL, "attn_decode_static: batch and heads are limited to 65535 (grid dimensions), max_ctx to 2^30");
   if (!q || !k_cache || !v_cache || !pos || !out) return fail(B200_EINVAL, "attn_decode_static: null pointer");
   const int64_t nsplit = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+  // (B, nh <= 65535 and nsplit <= 2^23: the product below cannot overflow 64 bits)
   if (B * nh * nsplit > kStaticAttnSlots)
     return fail(B200_EINVAL,
                 "attn_decode_static: batch %lld x heads %lld x %lld chunks of 128 tokens = %lld partial results, the built-in "
@@ -647,7 +657,7 @@ int b200_attn_decode_static(const void* q, const void* k_cache, const void* v_ca
       return fail(B200_ELAUNCH, "attn_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
     scratch_of_device[dev] = ptr;
   }
-  return b200_attn_decode(q, k_cache, v_cache, pos, out, scratch_of_device[dev], B, nh, max_ctx, stream);
+  return b200_attn_decode(q, k_cache, v_cache, pos, out, scratch_of_device[dev], B, nh, max_ctx, flags, stream);
 }
 
 int b200_silu_mul(const void* gu, void* out, int64_t B, int64_t I, void* stream) {

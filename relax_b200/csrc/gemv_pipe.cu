@@ -132,7 +132,6 @@ struct XLayout {
 
 enum { kPrologueNone = 0, kPrologueRmsNorm = 1, kPrologueSwiGLU = 2 };
 constexpr int kMaxPeers = 8;
-constexpr uint64_t kPeerWaitNs = 2000000000ull;          // 2 s for the other GPUs to publish their partial results
 
 // Sum over tensor-parallel ranks fused into a row-parallel matmul.  y (this rank's partial result)
 // lives in memory that every peer has mapped; the CTA that finishes last on this GPU publishes a
@@ -148,6 +147,7 @@ struct PeerReduce {
   const int* epoch = nullptr;               // device scalar: flags carry *epoch + 1 (grows from step to step)
   int* done_counter = nullptr;              // zero between launches
   __half* out = nullptr;                    // [M, N] fp16, local
+  uint64_t wait_ns = 2000000000ull;         // how long to wait for the other GPUs' flags (option gemv.peer_wait_ms)
 };
 
 struct PipeParams {
@@ -325,7 +325,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         const int* f = p.red.peer_flags[p.red.rank] + p.red.flag_base + lane;
         const uint64_t t0 = globaltimer_ns();
         while (ld_acquire_sys(f) < e) {
-          if (globaltimer_ns() - t0 > kPeerWaitNs) {   // a rank never published: give up, flag the error
+          if (globaltimer_ns() - t0 > p.red.wait_ns) {   // a rank never published: give up, flag the error
             atomicExch(&g_gemv_pipe_error, 16);
             break;
           }
@@ -818,6 +818,7 @@ PeerReduce make_reduce(const B200PeerReduce* r) {
   red.epoch = static_cast<const int*>(r->epoch);
   red.done_counter = static_cast<int*>(r->done_counter);
   red.out = static_cast<__half*>(r->out);
+  red.wait_ns = (uint64_t)options().gemv_peer_wait_ms * 1000000ull;
   return red;
 }
 

@@ -225,7 +225,9 @@ class DecodeEngine:
                                               self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), B, self.nh_local,
                                               self.max_ctx, sp))
             self._check(L.b200_attn_decode(self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.pos.data_ptr(),
-                                           self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx, sp))
+                                           self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx,
+                                           _lib.ATTN_EARLY_KV_LOADS,   # rope_kv_append sits directly in front and waits first
+                                           sp))
         if self.peer is not None:
             d = self._reduce_desc(0, i, self.o)
             self._check(L.b200_q4f16_gemv_allreduce(self.attn.data_ptr(), w["o"][0].data_ptr(), w["o"][1].data_ptr(),

@@ -93,7 +93,7 @@ def test_rope_append_attention(cuda_lib, B, nh, ctx, max_ctx):
     scratch = torch.empty(nbytes // 4, dtype=torch.float32, device="cuda")
     out = torch.empty((B, nh * D), dtype=torch.float16, device="cuda")
     assert cuda_lib.b200_attn_decode(q_out.data_ptr(), tk.data_ptr(), tv.data_ptr(), tpos.data_ptr(), out.data_ptr(),
-                                     scratch.data_ptr(), B, nh, max_ctx, 0) == 0, _lib.last_error()
+                                     scratch.data_ptr(), B, nh, max_ctx, 0, 0) == 0, _lib.last_error()
     torch.cuda.synchronize()
     ref = odec.attention_decode(q_out.cpu().numpy(), tk.cpu().numpy(), tv.cpu().numpy(), ctx)
     close(out.cpu().numpy(), ref, 4e-3, 2e-3, "attention")

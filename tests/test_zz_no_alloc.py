@@ -19,11 +19,11 @@ def _run(L, fn_static, B, nh, ctx, max_ctx, seed):
     pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
     out = torch.full((B, nh * 128), float("nan"), dtype=torch.float16, device="cuda")
     if fn_static:
-        rc = L.b200_attn_decode_static(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), out.data_ptr(), B, nh, max_ctx, 0)
+        rc = L.b200_attn_decode_static(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), out.data_ptr(), B, nh, max_ctx, 0, 0)
     else:
         scratch = torch.empty(L.b200_attn_decode_scratch_bytes(B, nh, max_ctx) // 4, dtype=torch.float32, device="cuda")
         rc = L.b200_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), out.data_ptr(), scratch.data_ptr(),
-                                B, nh, max_ctx, 0)
+                                B, nh, max_ctx, 0, 0)
     assert rc == 0, _lib.last_error()
     torch.cuda.synchronize()
     return out.cpu().numpy()
@@ -44,6 +44,6 @@ def test_static_scratch_attention_matches_caller_scratch(cuda_lib):
 def test_static_scratch_attention_rejects_oversize(cuda_lib):
     t = torch.zeros(8, dtype=torch.float16, device="cuda")
     # 64 sequences x 32 heads x 16 chunks = 32768 partial results > 8192: refused before any launch
-    rc = cuda_lib.b200_attn_decode_static(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 64, 32, 2048, 0)
+    rc = cuda_lib.b200_attn_decode_static(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 64, 32, 2048, 0, 0)
     assert rc == _lib.EINVAL
     assert "8192" in _lib.last_error()
