@@ -102,7 +102,7 @@ class DecodeEngine:
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
                  device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True,
-                 fused_attention=False):
+                 fused_attention=False, guard=None, verify: bool = True):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
@@ -111,6 +111,11 @@ class DecodeEngine:
         self.nh_local = cfg.heads // world
         if cfg.heads % world:
             raise ValueError("heads must divide by the tensor-parallel size")
+        # host-side checks of the tensor-parallel set-up: shard shapes agree across ranks before anything is
+        # launched; `guard` (tp.StepGuard on a CPU-capable group) is consulted before every eager step
+        self.guard = guard
+        if world > 1 and verify and layers:
+            tp.verify_sharding(layers, rank, world, cfg.hidden, cfg.inter, group=group)
         f16 = dict(dtype=torch.float16, device=self.device)
         hl = H // world
         il_max = max(l["inter_local"] for l in layers) if layers else cfg.inter
@@ -265,6 +270,8 @@ class DecodeEngine:
         self.pos, writes logits (when there is an lm_head), samples greedily into self.tokens and
         advances self.pos.  All inputs live on the device, so the step can be captured and replayed."""
         cfg, L, B = self.cfg, self.L, self.batch
+        if self.guard is not None and not torch.cuda.is_current_stream_capturing():
+            self.guard.check()
         sp = torch.cuda.current_stream(self.device).cuda_stream
         self._check(L.b200_embed_rows(self.embed.data_ptr(), self.tokens.data_ptr(), self.x.data_ptr(), B, cfg.hidden,
                                       self.embed.shape[0], sp))

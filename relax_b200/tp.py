@@ -89,3 +89,93 @@ def shard_layer(full: dict, rank: int, world: int, hidden: int, inter: int):
     a, b = shard_k(wq, s, i0, i1)
     out["down"] = (_contig(a), _contig(b))
     return out
+
+
+# ---------------------------------------------------------------------------------- host-side checks
+class ShardingMismatch(ValueError):
+    """The ranks of a tensor-parallel group hold shards that do not fit together."""
+
+
+class RankLeft(RuntimeError):
+    """A rank of the tensor-parallel group announced that it is leaving (or stopped answering)."""
+
+
+def shard_signature(shard: dict, hidden: int, inter_range=None):
+    """What the other ranks need to know about one rank's layer shard: its sizes as integers."""
+    def shape(a):
+        return [int(d) for d in a.shape]
+
+    sig = [int(shard["hidden_local"]), int(shard["inter_local"]), int(hidden)]
+    for key in ("qkv", "o", "gu", "down"):
+        sig += shape(shard[key][0]) + shape(shard[key][1])
+    return sig
+
+
+def verify_sharding(shards, rank: int, world: int, hidden: int, inter: int, group=None):
+    """Checks on the host, before anything is launched, that every rank's layer shards fit together:
+    equal head slices, local shapes consistent with hidden_local / inter_local, and K slices of the
+    row-parallel matmuls that add up to `inter`.  Every rank gathers every rank's sizes
+    (torch.distributed.all_gather_object on `group`, any backend) and raises ShardingMismatch on ALL
+    ranks when something disagrees, so no rank goes on to a collective the others never join."""
+    import torch.distributed as dist
+
+    mine = [shard_signature(s, hidden) for s in shards]
+    if world > 1:
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+    else:
+        everyone = [mine]
+    problems = []
+    nl = len(mine)
+    for r, sigs in enumerate(everyone):
+        if len(sigs) != nl:
+            problems.append(f"rank {r} holds {len(sigs)} layers, rank {rank} holds {nl}")
+            continue
+        for li, sig in enumerate(sigs):
+            hl, il, h = sig[0], sig[1], sig[2]
+            want = [hl, il, h,
+                    3 * hl, h // 8, 3 * hl, h // 32,        # qkv
+                    h, hl // 8, h, hl // 32,                # o
+                    2 * il, h // 8, 2 * il, h // 32,        # gate | up
+                    h, il // 8, h, il // 32]                # down
+            if h != hidden or hl * world != hidden:
+                problems.append(f"rank {r} layer {li}: hidden {h} / hidden_local {hl} do not give {hidden} over {world} ranks")
+            elif sig != want:
+                problems.append(f"rank {r} layer {li}: shard shapes {sig[3:]} do not match hidden_local {hl}, inter_local {il}")
+    for li in range(nl):
+        if all(len(s) == nl for s in everyone):
+            tot = sum(s[li][1] for s in everyone)
+            if tot != inter:
+                problems.append(f"layer {li}: the ranks' K slices of the down projection add up to {tot}, not {inter}")
+    if problems:
+        raise ShardingMismatch("; ".join(problems[:4]))
+
+
+class StepGuard:
+    """Host-side liveness check between decode steps.  Every rank calls check() before it launches a
+    step: one tiny all-reduce (MIN of "I am staying") on a CPU-capable process group.  A rank that
+    wants to leave calls leave() INSTEAD of check(), between steps, with none of its kernels or
+    collectives in flight; the others then get RankLeft from the same collective and launch nothing.
+    A rank that disappears without announcing it makes the collective fail or time out (the group's
+    timeout), which is reported as RankLeft too.  Nothing here touches a GPU."""
+
+    def __init__(self, group=None):
+        self.group = group
+
+    def _exchange(self, staying: int) -> int:
+        import torch
+        import torch.distributed as dist
+
+        t = torch.tensor([staying], dtype=torch.int32)
+        try:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        except Exception as e:  # a peer that is gone: connection closed, or the group's timeout ran out
+            raise RankLeft(f"a rank of the group stopped answering: {e}") from e
+        return int(t.item())
+
+    def check(self):
+        if self._exchange(1) != 1:
+            raise RankLeft("a rank of the tensor-parallel group has left; no further step is launched")
+
+    def leave(self):
+        self._exchange(0)

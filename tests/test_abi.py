@@ -26,7 +26,7 @@ def test_header_symbols_all_exported_and_bound():
     for s in syms:
         assert hasattr(handle, s), f"{s} declared in include/b200_q4f16.h but not exported"
     assert sorted(_lib.PROTOTYPES) == syms, "ctypes prototypes out of sync with the header"
-    assert _lib.lib().b200_abi_version() == 100
+    assert _lib.lib().b200_abi_version() == 101
 
 
 def _cpu_case(m=2, n=16, k=64):

@@ -1,5 +1,9 @@
-"""Tensor-parallel sharding checked on the CPU: two gloo ranks, each computing its shard with the
-oracle, must reproduce the unsharded oracle after the one all-reduce per row-parallel matmul."""
+"""Tensor-parallel sharding checked on the CPU: gloo ranks (2, 4 and 8, the last two with an uneven
+K split like 11008's), each computing its shard with the oracle, must reproduce the unsharded oracle
+after the one all-reduce per row-parallel matmul.  Plus the host-side failure handling: shard shapes
+that disagree across ranks, and a rank that leaves between steps, end in an error on every remaining
+rank instead of a hang."""
+import datetime
 import os
 import socket
 
@@ -45,14 +49,16 @@ def test_shard_shapes():
     assert tot_i == cfg.inter
 
 
-def _rank_main(rank, world, port, ret):
+def _rank_main(rank, world, port, ret, hidden, heads, inter):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["OMP_NUM_THREADS"] = "1"          # one oracle thread per rank: the ranks share the host's cores
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        cfg = decoder.DecoderConfig(hidden=512, heads=4, inter=768, layers=1, vocab=10)
+        cfg = decoder.DecoderConfig(hidden=hidden, heads=heads, inter=inter, layers=1, vocab=10)
         full = decoder.synth_layer_numpy(cfg, 3)
         sh = tp.shard_layer(full, rank, world, cfg.hidden, cfg.inter)
+        tp.verify_sharding([sh], rank, world, cfg.hidden, cfg.inter)
         rng = np.random.default_rng(0)
         B, max_ctx, pos, D = 2, 8, 3, 128
         x = rng.standard_normal((B, cfg.hidden)).astype(np.float16)
@@ -94,13 +100,99 @@ def _rank_main(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_sharded_layer_matches_unsharded_gloo():
+def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
+        return s.getsockname()[1]
+
+
+# inter 2816 = 11 blocks of 256: 3,3,3,2 over 4 ranks and 2,2,2,1,1,1,1,1 over 8 (the same kind of uneven split
+# that 11008 = 43 blocks gets)
+@pytest.mark.parametrize("world,hidden,heads,inter", [(2, 512, 4, 768), (4, 2048, 16, 2816), (8, 2048, 16, 2816)])
+def test_sharded_layer_matches_unsharded_gloo(world, hidden, heads, inter):
+    sizes = [b - a for a, b in tp.split_blocks(inter, world)]
+    if world == 4:
+        assert sizes == [768, 768, 768, 512]
+    if world == 8:
+        assert sizes == [512, 512, 512, 256, 256, 256, 256, 256]
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_rank_main, args=(2, port, ret), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(world, _free_port(), ret, hidden, heads, inter), nprocs=world, join=True)
     e1, e2 = ret["err"]
     # only the fp32 summation order and fp16 roundings at op boundaries differ
     assert e1 < 2e-3 and e2 < 4e-3, (e1, e2)
+
+
+def _mismatch_main(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = decoder.DecoderConfig(hidden=512, heads=4, inter=768, layers=1, vocab=10)
+        full = decoder.synth_layer_numpy(cfg, 3)
+        # rank 1 was sharded from a model with another intermediate size: the K slices of the down projection
+        # (512 + 512) no longer add up to 768
+        if rank == 1:
+            other = decoder.DecoderConfig(hidden=512, heads=4, inter=1024, layers=1, vocab=10)
+            sh = tp.shard_layer(decoder.synth_layer_numpy(other, 3), rank, world, other.hidden, other.inter)
+        else:
+            sh = tp.shard_layer(full, rank, world, cfg.hidden, cfg.inter)
+        try:
+            tp.verify_sharding([sh], rank, world, cfg.hidden, cfg.inter)
+            ret[rank] = "no error"
+        except tp.ShardingMismatch as e:
+            ret[rank] = "mismatch: " + str(e)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_disagreeing_shard_shapes_raise_on_every_rank():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_mismatch_main, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert all(str(ret[r]).startswith("mismatch") for r in range(2)), dict(ret)
+    assert "add up to" in ret[0]
+
+
+def _leaver_main(rank, world, port, ret, announce):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    guard = tp.StepGuard()
+    steps_done = 0
+    try:
+        for step in range(4):
+            if rank == world - 1 and step == 2:
+                # this rank leaves between steps, with nothing of its own in flight
+                if announce:
+                    guard.leave()
+                ret[rank] = ("left", steps_done)
+                return
+            guard.check()                      # raises RankLeft instead of launching the step
+            t = torch.ones(4)
+            dist.all_reduce(t)                 # the step's own collective
+            assert float(t[0]) == world
+            steps_done += 1
+        ret[rank] = ("finished", steps_done)
+    except tp.RankLeft as e:
+        ret[rank] = ("rank_left", steps_done)
+    finally:
+        if not (rank == world - 1 and not announce):
+            try:
+                dist.destroy_process_group()
+            except Exception:
+                pass
+
+
+@pytest.mark.parametrize("announce", [True, False])
+def test_rank_leaving_between_steps_is_an_error_not_a_hang(announce):
+    world = 3
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    ctx = mp.spawn(_leaver_main, args=(world, _free_port(), ret, announce), nprocs=world, join=False)
+    import time
+
+    t0 = time.time()
+    while not ctx.join(timeout=5):
+        assert time.time() - t0 < 120, "ranks still running: the remaining ranks hang"
+    assert ret[world - 1] == ("left", 2)
+    for r in range(world - 1):
+        assert ret[r] == ("rank_left", 2), dict(ret)
