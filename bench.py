@@ -268,7 +268,7 @@ def run_decode(args, world, rank, dev, batches):
         eng = decoder.DecodeEngine(cfg, layers, embed, final_norm, lm_head, batch, max_ctx, dev, rank, world,
                                    peer_reduce=not args.decode_nccl,
                                    fused_attention="rope" if args.decode_attn2 else args.decode_attn1)
-        bp = min(batch, 2)                                            # sequences checked by the parity step
+        bp = min(batch, 4)                                            # sequences checked by the parity step
         ref = None
         if rank == 0 and not args.no_decode_parity:
             ref = decoder.DecodeEngine(cfg, full_layers, embed, final_norm, embed, bp, max_ctx, dev, 0, 1, fused=False,
@@ -333,7 +333,7 @@ def run_decode(args, world, rank, dev, batches):
             raise RuntimeError(f"device error flags {err:#x} after the decode run")
 
         # ---- parity of one step (outside every timed region)
-        parity = None
+        parity, parity_rows, parity_overflow = None, 0, 0
         if not args.no_decode_parity:
             barrier()
             with torch.cuda.stream(stream):
@@ -349,7 +349,16 @@ def run_decode(args, world, rank, dev, batches):
                     ref.step()
                     stream.synchronize()
                 want = ref.logits.float()
-                parity = float((got - want).abs().max() / want.abs().max())
+                # A random-init model with these weight statistics overflows fp16 in the residual stream for some
+                # token sequences (the CPU oracle does the same: fp16 semantics, not a kernel property).  Such a
+                # sequence must be non-finite in BOTH engines; the others are compared.
+                ok_g, ok_w = torch.isfinite(got).all(dim=1), torch.isfinite(want).all(dim=1)
+                parity_overflow = int((~ok_g & ~ok_w).sum())
+                if bool((ok_g != ok_w).any()):
+                    parity = 1.0                                      # one engine overflowed where the other did not
+                elif bool(ok_w.any()):
+                    parity_rows = int(ok_w.sum())
+                    parity = float(((got[ok_w] - want[ok_w]).abs().amax(dim=1) / want[ok_w].abs().amax(dim=1)).max())
             barrier()
 
         # weights + KV + lm_head actually read per token by one rank
@@ -370,8 +379,9 @@ def run_decode(args, world, rank, dev, batches):
             "allreduce": (None if world == 1 else "fused into the o/down matmul kernels over NVLink peer memory (fp16 partials, "
                           "rank-order sum)" if eng.peer is not None else "NCCL fp16, 2 per layer"), "steps": steps,
             "parity_max_rel": parity,
-            "parity_against": None if parity is None else
-            f"one-GPU engine on rank 0 (unfused kernels, same seeds), logits of the first {bp} sequence(s) at position {parity_pos}",
+            "parity_against": None if args.no_decode_parity else
+            f"one-GPU engine on rank 0 (unfused kernels, same seeds), logits of the first {bp} sequence(s) at position {parity_pos}: "
+            f"{parity_rows} compared, {parity_overflow} overflow fp16 in both engines alike",
             "scaling_efficiency": (value / (world * n1[str(batch)]) if world > 1 and str(batch) in n1 else None),
         }
         results.append(out)
