@@ -18,7 +18,7 @@ LIB = os.path.join(HERE, "libb200_q4f16.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 SOURCES = ["capi.cu", "tmap.cu", "dequant.cu", "gemv.cu", "gemv_pipe.cu", "gemm_tcgen05.cu", "gemm_ws_tcgen05.cu", "decoder_ops.cu"]
-HEADERS = ["internal.h", "q4_common.cuh", "sm100_ptx.cuh", "tmap.h"]
+HEADERS = ["internal.h", "q4_common.cuh", "sm100_ptx.cuh", "tmap.h", "skinny_common.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

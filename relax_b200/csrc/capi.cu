@@ -257,6 +257,7 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "gemv.stages")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.stages in 0..16"); o.gemv_stages = v; }
   else if (!strcmp(name, "gemv.pdl")) { o.gemv_pdl = v != 0; }
   else if (!strcmp(name, "gemv.ctas_per_sm")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemv.ctas_per_sm in 0..8"); o.gemv_ctas_per_sm = v; }
+  else if (!strcmp(name, "gemv.exact")) { o.gemv_exact = v != 0; }
   else if (!strcmp(name, "gemv.peer_wait_ms")) { if (v < 1 || v > 60000) return fail(B200_EINVAL, "gemv.peer_wait_ms in 1..60000"); o.gemv_peer_wait_ms = v; }
   else if (!strcmp(name, "gemm.ws_ksplit")) { if (v < 0 || v > 8 || (v & (v - 1))) return fail(B200_EINVAL, "gemm.ws_ksplit is 0, 1, 2, 4 or 8"); o.gemm_ws_ksplit = v; }
   else if (!strcmp(name, "gemm.ws_max_m")) { if (v < 0 || v > 128) return fail(B200_EINVAL, "gemm.ws_max_m in 0..128"); o.gemm_ws_max_m = v; }
@@ -273,6 +274,7 @@ int64_t b200_get_option(const char* name) {
   if (!strcmp(name, "gemv.stages")) return o.gemv_stages;
   if (!strcmp(name, "gemv.pdl")) return o.gemv_pdl;
   if (!strcmp(name, "gemv.ctas_per_sm")) return o.gemv_ctas_per_sm;
+  if (!strcmp(name, "gemv.exact")) return o.gemv_exact;
   if (!strcmp(name, "gemv.peer_wait_ms")) return o.gemv_peer_wait_ms;
   if (!strcmp(name, "gemm.max_ctas")) return o.gemm_max_ctas;
   if (!strcmp(name, "gemm.ws_ksplit")) return o.gemm_ws_ksplit;

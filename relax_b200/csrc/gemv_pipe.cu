@@ -32,10 +32,32 @@
 // and write y) wait.  Several CTAs fit on one SM, so the CTAs of the next launch move in as
 // those of the previous one leave and their first copies are in flight while it drains.
 //
+// Two arithmetic forms share the pipeline (template flag FAST):
+//
+//   exact  every weight is rounded to fp16 as the reference does, w = RN16((q-7) * s), before the
+//          fp32 accumulation: 1 shift + 4 LOP3 + 4 half2 ops + 4 HMUL2 per packed word.  Results
+//          differ from the reference only by the fp32 summation order.  Any batch 1..16.
+//   fast   (batch 1) the scale is applied to fp32 GROUP SUMS instead: y = sum_g s_g * sum_{k in g} x_k (q_k - 7).
+//          * The nibbles go to the tensor core as they come out of the LOP3, still carrying their
+//            magic-number offset (1024 + q for even k, 64 + q for odd k: both exact in fp16); the
+//            offset's share, C_g = sum_k x_k * (1031 | 71), is formed once per activation block
+//            while x is staged and enters the MMA as its (negated) accumulator input.
+//          * A lane keeps owning two whole groups (two 16-byte loads per row), and the eight
+//            columns of the MMA keep the groups apart: column c receives x only in the k slots
+//            that lane t = c supplies (B is zero everywhere else), so D[:, c] is the group sum of
+//            the group lane c holds.  Eight MMAs run into the same accumulator, then two FFMA per
+//            row apply the scales.
+//          1 shift + 4 LOP3 per packed word and 8 FFMA + 8 conversions per 16 words: about a third
+//          of the exact form's issue slots, which was its limit.
+//          The unrounded weight differs from the reference's by at most half an fp16 ulp, so
+//          |y - y_ref| <= 2^-11 * sum|x*w| (typically 3e-4 of the output's spread); an activation
+//          with a single 1.0 still reproduces the reference's weight bit for bit.
+//
 // Requires K % 256 == 0 and 16-byte aligned scales (tensor-map stride rules); other shapes use
 // the register-streaming kernel.
 #include "internal.h"
 #include "q4_common.cuh"
+#include "skinny_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tmap.h"
 
@@ -46,109 +68,14 @@ __device__ int g_gemv_pipe_error = 0;   // set when a bounded wait gives up
 namespace {
 
 using namespace ptx;
+using namespace skinny;
 
 constexpr int kRows = 16;                // rows per stage / row tile
 constexpr int kMaxStages = 8;
 constexpr uint64_t kConsumerWaitNs = 2000000000ull;     // 2 s: a stage copy takes microseconds
 constexpr uint64_t kProducerWaitNs = 30000000000ull;    // 30 s: may span the previous kernel's whole run
 
-__device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                            uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-
-// Eight fp16 at a time, fp32 inside, one round-to-nearest at the end (the same arithmetic as the
-// stand-alone RMSNorm and SwiGLU kernels).
-__device__ __forceinline__ uint4 add_f16x8(const uint4& a, const uint4& b) {
-  uint4 o;
-  const __half2* x = reinterpret_cast<const __half2*>(&a);
-  const __half2* y = reinterpret_cast<const __half2*>(&b);
-  __half2* r = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = __half22float2(x[j]), g = __half22float2(y[j]);
-    r[j] = __floats2half2_rn(f.x + g.x, f.y + g.y);
-  }
-  return o;
-}
-__device__ __forceinline__ uint4 scale_f16x8(const uint4& a, float inv, const uint4& w) {
-  uint4 o;
-  const __half2* x = reinterpret_cast<const __half2*>(&a);
-  const __half2* y = reinterpret_cast<const __half2*>(&w);
-  __half2* r = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = __half22float2(x[j]), g = __half22float2(y[j]);
-    r[j] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
-  }
-  return o;
-}
-__device__ __forceinline__ uint4 silu_mul_f16x8(const uint4& gate, const uint4& up) {
-  uint4 o;
-  const __half2* x = reinterpret_cast<const __half2*>(&gate);
-  const __half2* y = reinterpret_cast<const __half2*>(&up);
-  __half2* r = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 g = __half22float2(x[j]), u = __half22float2(y[j]);
-    r[j] = __floats2half2_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
-  }
-  return o;
-}
-
-// Layout of the staged x block: one 16-byte slot per (8-k word jw, batch column).  Lane (g,t)
-// reads column g of words 32c + 8t + i (i = 0..7), so the four lanes t of a row-group read
-// words 8 apart in the same instruction and their slots must differ mod 8:
-//   NC >= 8: NC slots per word, column XOR-ed with 2*((jw>>3)&3)  (= 2t);
-//   NC <  8: NC slots per word plus NC slots of padding after every 8 words.
-template <int NC>
-struct XLayout {
-  __device__ __forceinline__ static int slot(int jw, int col) {
-    if (NC >= 8) return jw * NC + (col ^ (((jw >> 3) & 3) << 1));
-    return NC * (jw + (jw >> 3)) + col;
-  }
-  // slots per 256-k chunk (32 words)
-  static constexpr int kSlotsPerChunk = NC >= 8 ? 32 * NC : 36 * NC;
-  // bytes for a block of `k` (multiple of 256)
-  __host__ __device__ static constexpr size_t bytes(int k) { return (size_t)(k / 256) * kSlotsPerChunk * 16; }
-};
-
 enum { kPrologueNone = 0, kPrologueRmsNorm = 1, kPrologueSwiGLU = 2 };
-constexpr int kMaxPeers = 8;
-
-// Sum over tensor-parallel ranks fused into a row-parallel matmul.  y (this rank's partial result)
-// lives in memory that every peer has mapped; the CTA that finishes last on this GPU publishes a
-// flag to every rank; every CTA then waits for all ranks' flags and adds up its slice of the
-// partial results in rank order (so every rank gets the same bits) into `out`.  Peer memory is
-// read with plain volatile loads only.
-struct PeerReduce {
-  int world = 0;                            // <= 1: off
-  int rank = 0;
-  const __half* peer_y[kMaxPeers] = {};     // rank r's partial result as mapped on this GPU (peer_y[rank] == y)
-  int* peer_flags[kMaxPeers] = {};          // rank r's flag array as mapped on this GPU
-  int flag_base = 0;                        // this reduction's `world` slots inside a flag array
-  const int* epoch = nullptr;               // device scalar: flags carry *epoch + 1 (grows from step to step)
-  int* done_counter = nullptr;              // zero between launches
-  __half* out = nullptr;                    // [M, N] fp16, local
-  uint64_t wait_ns = 2000000000ull;         // how long to wait for the other GPUs' flags (option gemv.peer_wait_ms)
-};
 
 struct PipeParams {
   CUtensorMap tm_w;   // uint32 {32, N, K/256}, box {32, 16, CH}, 128B swizzle
@@ -169,23 +96,29 @@ struct PipeParams {
 };
 
 // Shared memory carve-up (after rounding the base up to 1024 bytes):
-//   ring: nstages * kStageBytes
-//   bars: full[kMaxStages] empty[kMaxStages] red_full[kMaxStages+1] red_empty[kMaxStages+1]
-//   xs:   XLayout::bytes(kblk)     permuted x block
-//   red:  (nstages+1) * CW * MT*128 * 4   per-warp partial sums of a tile, one buffer per tile in flight
-//   accs: tiles_per_cta * MT*128*4 (only when K is cut into several blocks)
+//   ring:  nstages * kStageBytes
+//   bars:  full[kMaxStages] empty[kMaxStages] red_full[kMaxStages+1] red_empty[kMaxStages+1]
+//   xs:    XLayout::bytes(kblk)     permuted x block
+//   corr:  (fast form) 32 floats per 256-k chunk: minus the offset sum of each group, see corr_index()
+//   red:   (nstages+1) * CW * kOut * 4   per-warp partial sums of a tile, one buffer per tile in flight
+//   accs:  tiles_per_cta * kOut * 4 (only when K is cut into several blocks)
 //
 // Warps: CW consumers, then one TMA warp (two issuing lanes), then one epilogue warp.
-template <int NC, int CW, int CH, int PRO>
-__global__ void __launch_bounds__((CW + 2) * 32, 1)
+template <int NC, int CW, int CH, int PRO, bool FAST>
+__global__ void __launch_bounds__((CW + 2) * 32, FAST ? 2 : 1)
 q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   constexpr int MT = (NC + 7) / 8;
-  constexpr int kOut = MT * 128;           // outputs per row tile held in fragment order
+  static_assert(!FAST || NC == 1, "the fast form is the batch-1 kernel");
+  // outputs per row tile as one consumer warp leaves them: the exact form stores whole MMA fragments,
+  // the fast form one value per row (padded to two)
+  constexpr int NCP = 2;
+  constexpr int kOut = FAST ? kRows * NCP : MT * 128;
   constexpr int KC = 256 * CH;             // k per stage
   constexpr int kWBytes = CH * kRows * 128;           // [chunk][row][128 B], 128B-swizzled
   constexpr int kSBytes = CH * kRows * 16;            // [chunk][row][8 scales = 16 B]
   constexpr int kStageBytes = kWBytes + kSBytes;      // a multiple of 1024, as the swizzle needs
   constexpr int U = CH / CW;                          // chunks per warp per stage
+  using XL = XLayout<NC>;
   static_assert(CH % CW == 0 && U >= 1, "each consumer warp takes whole chunks");
   static_assert(kStageBytes % 1024 == 0, "stage alignment");
   extern __shared__ unsigned char smem_unaligned[];
@@ -197,11 +130,13 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   uint64_t* red_full = empty + kMaxStages;
   uint64_t* red_empty = red_full + kMaxStages + 1;
   uint4* xs = reinterpret_cast<uint4*>(red_empty + kMaxStages + 1);
-  float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + XLayout<NC>::bytes(p.kblk));
+  float* negcorr = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + XL::bytes(p.kblk));
+  float* red = negcorr + (FAST ? (p.kblk >> 8) * 32 : 0);
   const int nred = p.nstages + 1;
   float* accs = red + nred * CW * kOut;
 
   __shared__ int s_abort;                    // set once a bounded wait gives up: later waits are skipped
+  __shared__ uint4 s_zero;                   // fast form: what the lanes without an activation column feed the MMA
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -210,6 +145,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
 
   if (tid == 0) {
     s_abort = 0;
+    s_zero = make_uint4(0, 0, 0, 0);
     for (int s = 0; s < p.nstages; ++s) {
       mbar_init(&full[s], 2);
       mbar_init(&empty[s], CW);
@@ -282,8 +218,9 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         }
         const float* rbuf = red + rb * (CW * kOut);
 #pragma unroll
-        for (int q = 0; q < 4 * MT; ++q) {
+        for (int q = 0; q < (kOut + 31) / 32; ++q) {
           const int e = q * 32 + lane;
+          if (kOut % 32 != 0 && e >= kOut) break;
           float sum = 0.f;
 #pragma unroll
           for (int w2 = 0; w2 < CW; ++w2) sum += rbuf[w2 * kOut + e];
@@ -293,9 +230,15 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
             if (kb < nkb - 1) *a = sum;
           }
           if (kb == nkb - 1) {
-            const int i = q & 3, mt = q >> 2;
-            const int row = tile * kRows + (lane >> 2) + 8 * (i >> 1);
-            const int col = mt * 8 + 2 * (lane & 3) + (i & 1);
+            int row, col;
+            if (FAST) {
+              row = tile * kRows + e / NCP;      // [row][column] as the consumers stored it
+              col = e % NCP;
+            } else {
+              const int i = q & 3, mt = q >> 2;  // MMA fragment order
+              row = tile * kRows + (lane >> 2) + 8 * (i >> 1);
+              col = mt * 8 + 2 * (lane & 3) + (i & 1);
+            }
             if (row < p.N && col < p.M) p.y[(int64_t)col * p.N + row] = __float2half_rn(sum);
           }
         }
@@ -343,22 +286,37 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   constexpr int kConsumers = CW * 32;
 
   // Per-thread offsets inside a stage (chunk `warp`; further chunks of this warp are CW chunks on).
-  //   weights: row g at (chunk*16 + g)*128, 16-byte word j at ((j ^ g) << 4); row g+8 is 1024 on
-  //   (same swizzle phase).  Words 2t and 2t+1 differ in bit 4 only.
+  //   weights: row g at (chunk*16 + g)*128, 16-byte unit j at ((j ^ g) << 4); row g+8 is 1024 on
+  //   (same swizzle phase).
+  //   A lane owns 16-byte units 2t and 2t+1 (scale groups 2t, 2t+1 of the chunk), which differ in address
+  //   bit 4 only.
   const uint32_t w_off = (uint32_t)((warp * kRows + g) * 128 + (((2 * t) ^ g) << 4));
-  const uint32_t s_off = (uint32_t)(kWBytes + (warp * kRows + g) * 16 + t * 4);
+  //   scales: exact form one 32-bit pair (groups 2t, 2t+1) per row; fast form the four groups 4t'..4t'+3 of the
+  //   two output columns the lane holds (t' = t & 1; lanes t >= 2 hold columns that stay empty)
+  const uint32_t s_off = FAST ? (uint32_t)(kWBytes + (warp * kRows + g) * 16 + (t & 1) * 8)
+                              : (uint32_t)(kWBytes + (warp * kRows + g) * 16 + t * 4);
   // x: words 32*chunk + 8t + i of the staged block, column g (the k-block offset is added per stage).
-  // Lanes whose batch column does not exist (g >= NC) read column 0: what they feed into the MMA
-  // only reaches output columns >= NC, which are never stored.
-  const uint4* x_thr = xs + (NC >= 8 ? (warp * 32 + 8 * t) * NC + (g ^ (2 * t)) : NC * (warp * 36 + 9 * t) + (g < NC ? g : 0));
-  constexpr int kXStage = CH * XLayout<NC>::kSlotsPerChunk;   // slots per stage
-  constexpr int kXUnit = CW * XLayout<NC>::kSlotsPerChunk;    // slots between this warp's chunks
+  // Lanes whose batch column does not exist (g >= NC) read column 0: what they feed into the MMA only
+  // reaches output columns >= NC, which are never stored.  (Fast form: see x_own below.)
+  const int xcol = NC >= 8 ? g : (g < NC ? g : 0);
+  const uint4* x_thr = xs + (NC >= 8 ? (warp * 32 + 8 * t) * NC + (g ^ (2 * t)) : NC * (warp * 36 + 9 * t) + xcol);
+  constexpr int kXStage = CH * XL::kSlotsPerChunk;   // slots per stage
+  constexpr int kXUnit = CW * XL::kSlotsPerChunk;    // slots between this warp's chunks
+  // fast form: column c of the MMA is the group that lane t = c holds, so the activation goes into the B
+  // fragment of the lanes with g == t only (B[k slots of lane t][column g]); every other lane feeds zeros
+  const bool x_own = g == t;
+  const int x_mul = x_own ? 1 : 0;
+  // offset sums of the chunk: [t & 1][set] four floats each
+  const float4* c_thr = reinterpret_cast<const float4*>(negcorr) + warp * 8 + (t & 1) * 2;
+  constexpr int kCStage = CH * 8;                    // float4 per stage
+  constexpr int kCUnit = CW * 8;
 
   const Q4Consts qc = q4_consts();
-  pdl_wait();                                    // x may be the previous kernel's output
+  const uint32_t magic_hi = 0x54005400u;         // (64, 64): a nibble in mantissa bits 4..7 counts 1 per step
 
-  // Two accumulation chains over the whole tile: consecutive MMAs alternate between them so the
-  // tensor pipe never waits on its own result.
+  // exact form: two accumulation chains over the whole tile, consecutive MMAs alternate between them so the
+  // tensor pipe never waits on its own result.  fast form: acc[0] is the scaled total, the per-group sums
+  // live in registers of their own.
   float acc[2][MT][4];
 
   // One chunk (rows g and g+8, groups 2t and 2t+1) into the accumulators.  The weights are
@@ -388,10 +346,135 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     }
   };
 
+  // Fast form, the U chunks of one stage together.  Set h = 0 / 1 is the lane's 16-byte unit 2t / 2t+1 (an even /
+  // odd group); its four words for rows g and g+8 give eight MMAs into one accumulator d[u][h] that starts at
+  // minus the offset sums.  Afterwards d[u][h][0], [1] are row g's sums over groups 4t+h and 4t+2+h, [2], [3] row
+  // g+8's.  The MMAs are issued round-robin over the 2U accumulators (an MMA that follows the one it depends on
+  // waits out the tensor pipe's whole latency; with the accumulators interleaved nothing waits).
+  auto fast_stage = [&](const uint4 (&w)[U][2][2], const uint2 (&sc)[U][2], const uint4* xu, const float4* cu) {
+    float d[U][2][4];
+    const uint4* xb = x_own ? xu : &s_zero;
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+      uint32_t a[U][2][8];      // raw (offset) nibble pairs: [0..3] first MMA (rows g, g+8: even k, odd k), [4..7] second
+      uint4 b[U][2];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t w0 = wd == 0 ? w[u][0][h].x : wd == 1 ? w[u][0][h].y : wd == 2 ? w[u][0][h].z : w[u][0][h].w;
+          const uint32_t w1 = wd == 0 ? w[u][1][h].x : wd == 1 ? w[u][1][h].y : wd == 2 ? w[u][1][h].z : w[u][1][h].w;
+          b[u][h] = xb[x_mul * (u * kXUnit + 4 * h + wd)];      // (lanes that own no column all read one zero slot)
+          a[u][h][0] = lop3_and_or(w0, qc.lo, qc.magic);
+          a[u][h][1] = lop3_and_or(w1, qc.lo, qc.magic);
+          a[u][h][2] = lop3_and_or(w0, qc.hi, magic_hi);
+          a[u][h][3] = lop3_and_or(w1, qc.hi, magic_hi);
+          const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+          a[u][h][4] = lop3_and_or(w0s, qc.lo, qc.magic);
+          a[u][h][5] = lop3_and_or(w1s, qc.lo, qc.magic);
+          a[u][h][6] = lop3_and_or(w0s, qc.hi, magic_hi);
+          a[u][h][7] = lop3_and_or(w1s, qc.hi, magic_hi);
+        }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (wd == 0) {
+            const float4 c = cu[u * kCUnit + h];
+            mma_16x8x16_c(d[u][h], a[u][h][0], a[u][h][1], a[u][h][2], a[u][h][3], b[u][h].x, b[u][h].y, c.x, c.y, c.z, c.w);
+          } else {
+            mma_16x8x16(d[u][h], a[u][h][0], a[u][h][1], a[u][h][2], a[u][h][3], b[u][h].x, b[u][h].y);
+          }
+        }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          mma_16x8x16(d[u][h], a[u][h][4], a[u][h][5], a[u][h][6], a[u][h][7], b[u][h].z, b[u][h].w);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      // scales of groups 4t'+0..3: (s0, s1) (s2, s3); even groups belong to set 0, odd ones to set 1
+      const float2 g01 = __half22float2(u32_as_h2(sc[u][0].x)), g23 = __half22float2(u32_as_h2(sc[u][0].y));
+      const float2 h01 = __half22float2(u32_as_h2(sc[u][1].x)), h23 = __half22float2(u32_as_h2(sc[u][1].y));
+      acc[0][0][0] = fmaf(g01.x, d[u][0][0], acc[0][0][0]);
+      acc[0][0][0] = fmaf(g23.x, d[u][0][1], acc[0][0][0]);
+      acc[1][0][0] = fmaf(g01.y, d[u][1][0], acc[1][0][0]);
+      acc[1][0][0] = fmaf(g23.y, d[u][1][1], acc[1][0][0]);
+      acc[0][0][2] = fmaf(h01.x, d[u][0][2], acc[0][0][2]);
+      acc[0][0][2] = fmaf(h23.x, d[u][0][3], acc[0][0][2]);
+      acc[1][0][2] = fmaf(h01.y, d[u][1][2], acc[1][0][2]);
+      acc[1][0][2] = fmaf(h23.y, d[u][1][3], acc[1][0][2]);
+    }
+  };
+  // Fast form: this warp's share of stage `s` into registers; the stage goes back to the producer at once.
+  auto fast_load = [&](int s, uint32_t round, uint4 (&w)[U][2][2], uint2 (&sc)[U][2]) {
+    // On a timeout the kernel keeps going without waiting (results are garbage, the error flag says so) so
+    // that every warp still reaches the named barriers and the CTA ends.
+    if (!mbar_try_wait(&full[s], round & 1)) {
+      if (!*(volatile int*)&s_abort && !mbar_wait_ns(&full[s], round & 1, kConsumerWaitNs)) {
+        atomicExch(&g_gemv_pipe_error, 2);
+        *(volatile int*)&s_abort = 1;
+      }
+    }
+    const unsigned char* st = ring + (size_t)s * kStageBytes;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const unsigned char* su = st + u * (CW * kRows * 128);
+      w[u][0][0] = *reinterpret_cast<const uint4*>(su + w_off);
+      w[u][0][1] = *reinterpret_cast<const uint4*>(su + (w_off ^ 16u));
+      w[u][1][0] = *reinterpret_cast<const uint4*>(su + w_off + 1024);
+      w[u][1][1] = *reinterpret_cast<const uint4*>(su + (w_off ^ 16u) + 1024);
+      const unsigned char* ss = st + u * (CW * kRows * 16);
+      sc[u][0] = *reinterpret_cast<const uint2*>(ss + s_off);
+      sc[u][1] = *reinterpret_cast<const uint2*>(ss + s_off + 128);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      pin_loaded(w[u][0][0]);
+      pin_loaded(w[u][0][1]);
+      pin_loaded(w[u][1][0]);
+      pin_loaded(w[u][1][1]);
+      pin_loaded(sc[u][0].x);
+      pin_loaded(sc[u][0].y);
+      pin_loaded(sc[u][1].x);
+      pin_loaded(sc[u][1].y);
+    }
+    fence_proxy_async_smem();   // generic reads ordered before the TMA refill (async proxy)
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);            // all of this warp's share is in registers
+  };
+
+  // Stores one staged word (eight activations of one batch column) in the permuted order the unpack
+  // produces; the fast form also returns its offset sum.
+  auto stage_word = [&](int j, int m, const uint4& v) -> float {
+    uint4 q;
+    q.x = __byte_perm(v.x, v.z, 0x5410);
+    q.y = __byte_perm(v.x, v.z, 0x7632);
+    q.z = __byte_perm(v.y, v.w, 0x5410);
+    q.w = __byte_perm(v.y, v.w, 0x7632);
+    xs[XL::slot(j, m)] = q;
+    return FAST ? offset_sum_f16x8(v) : 0.f;
+  };
+  // Fast form (one batch column): minus the offset sum of scale group `grp`, twice (rows g and g+8 of the
+  // accumulator fragment).
+  auto store_group_sum = [&](int grp, float psum) {
+    const int ci = corr_index(grp);
+    negcorr[ci] = -psum;
+    negcorr[ci + 2] = -psum;
+  };
+
   int s = 0;                                     // ring slot of the current stage
   uint32_t round = 0;                            // how many times the ring has wrapped
   int rb = 0;                                    // reduction buffer of the current tile
   uint32_t rround = 0;
+  // Fast form: the weights never depend on the previous kernel, and with its CTAs resident beside the previous
+  // launch's they are in shared memory long before that kernel ends; so this warp's share of the FIRST stage is
+  // already in registers when the wait for the activations returns.
+  uint4 fw[U][2][2];
+  uint2 fsc[U][2];
+  if (FAST) fast_load(0, 0, fw, fsc);
+  pdl_wait();                                    // x may be the previous kernel's output
   // ---- RMSNorm prologue: r = fp16(x + delta), inv[m] = rsqrt(mean(r^2) + eps) for every row ------
   // Every CTA computes the statistics itself (K values per row: nothing next to its share of W);
   // CTA 0 also writes r out as the updated residual stream.
@@ -487,15 +570,16 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int j = tid + r * kConsumers;
-      if (j >= words) continue;
+      if (j >= words) continue;              // (words is a multiple of 32: whole warps leave together)
       uint4 v = make_uint4(0, 0, 0, 0);
       if (j * 8 < p.K) v = scale_f16x8(rms_keep[r], inv, rms_w[r]);
-      uint4 q;
-      q.x = __byte_perm(v.x, v.z, 0x5410);
-      q.y = __byte_perm(v.x, v.z, 0x7632);
-      q.z = __byte_perm(v.y, v.w, 0x5410);
-      q.w = __byte_perm(v.y, v.w, 0x7632);
-      xs[XLayout<NC>::slot(j, 0)] = q;
+      float psum = stage_word(j, 0, v);
+      if (FAST) {
+        // a group's four words sit in four consecutive lanes (words are dealt out in order, 32 per warp and round)
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        if ((j & 3) == 0) store_group_sum(j >> 2, psum);
+      }
     }
   }
   for (int kb = 0; kb < nkb; ++kb) {
@@ -503,10 +587,50 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     const int k_hi = min(p.K, k_lo + p.kblk);
     // ---- stage x[:, k_lo .. k_lo + kblk) permuted per 8 k; zero beyond K and beyond M --------------
     if (kb > 0) bar_sync(1, kConsumers);         // everyone is done reading the previous block
-    if (!(PRO == kPrologueRmsNorm && rms_one_pass)) {
+    if (FAST && !(PRO == kPrologueRmsNorm && rms_one_pass)) {
+      // one batch column: a thread takes a whole scale group (four words, 64 contiguous bytes), so its offset sum
+      // needs no exchange; all loads of a thread are issued before the first use
+      const int groups = p.kblk >> 5;
+      for (int grp = tid; grp < groups; grp += kConsumers) {
+        const int k = k_lo + grp * 32;
+        uint4 a[4], b[4], c[4];
+        const bool live = k < p.K;
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+          a[wd] = b[wd] = c[wd] = make_uint4(0, 0, 0, 0);
+          if (live) {
+            if (PRO == kPrologueSwiGLU) {
+              a[wd] = *reinterpret_cast<const uint4*>(p.x + k + 8 * wd);
+              b[wd] = *reinterpret_cast<const uint4*>(p.x + p.K + k + 8 * wd);
+            } else {
+              a[wd] = *reinterpret_cast<const uint4*>(p.x + k + 8 * wd);
+              if (PRO == kPrologueRmsNorm) {
+                if (p.delta) b[wd] = *reinterpret_cast<const uint4*>(p.delta + k + 8 * wd);
+                c[wd] = *reinterpret_cast<const uint4*>(p.norm_w + k + 8 * wd);
+              }
+            }
+          }
+        }
+        float psum = 0.f;
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+          uint4 v = a[wd];
+          if (live) {
+            if (PRO == kPrologueSwiGLU) {
+              v = silu_mul_f16x8(a[wd], b[wd]);
+            } else if (PRO == kPrologueRmsNorm) {
+              if (p.delta) v = add_f16x8(v, b[wd]);
+              v = scale_f16x8(v, s_inv[0], c[wd]);
+            }
+          }
+          psum += stage_word(4 * grp + wd, 0, v);
+        }
+        store_group_sum(grp, psum);
+      }
+    } else if (!(PRO == kPrologueRmsNorm && rms_one_pass)) {
       // four items per thread and round: all loads of a round are issued before the first use
       const int words = p.kblk >> 3;
-      const int items = words * NC;
+      const int items = words * NC;              // a multiple of 32: a warp's 32 items are all inside or all outside
       // (registers: small batches keep two CTAs per SM; without a prologue only one array is live)
       constexpr int R = NC >= 8 ? 4 : (PRO == kPrologueNone ? 4 : (NC == 1 ? 2 : 1));
       for (int i0 = tid; i0 < items; i0 += kConsumers * R) {
@@ -547,17 +671,11 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
               v = scale_f16x8(v, s_inv[m], c[r]);
             }
           }
-          uint4 q;
-          q.x = __byte_perm(v.x, v.z, 0x5410);
-          q.y = __byte_perm(v.x, v.z, 0x7632);
-          q.z = __byte_perm(v.y, v.w, 0x5410);
-          q.w = __byte_perm(v.y, v.w, 0x7632);
-          xs[XLayout<NC>::slot(j, m)] = q;
+          stage_word(j, m, v);
         }
       }
     }
     bar_sync(1, kConsumers);
-
     for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
@@ -565,7 +683,14 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         for (int i = 0; i < 4; ++i) acc[0][mt][i] = acc[1][mt][i] = 0.f;
 
       const uint4* xk = x_thr;
-      for (int k0 = k_lo; k0 < k_hi; k0 += KC, xk += kXStage, s = (s + 1 == p.nstages ? 0 : s + 1), round += (s == 0)) {
+      const float4* ck = c_thr;
+      for (int k0 = k_lo; k0 < k_hi; k0 += KC, xk += kXStage, ck += kCStage, s = (s + 1 == p.nstages ? 0 : s + 1), round += (s == 0)) {
+        if (FAST) {
+          // (the first stage of the launch is in registers already)
+          if (!(kb == 0 && tile == (int)blockIdx.x && k0 == k_lo)) fast_load(s, round, fw, fsc);
+          // chunks past K were zero-filled, their activations and offset sums staged as zeros: they add nothing
+          fast_stage(fw, fsc, xk, ck);
+        } else {
         // On a timeout the kernel keeps going without waiting (results are garbage, the error
         // flag says so) so that every warp still reaches the named barriers and the CTA ends.
         if (!mbar_try_wait(&full[s], round & 1)) {
@@ -612,6 +737,7 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
           for (int u = 0; u < U; ++u)
             if (k0 + (warp + u * CW) * 256 < k_hi) chunk(w[u], sc[u], xk + u * kXUnit);
         }
+        }
       }
 
       // ---- hand this warp's partial sums of the tile to the epilogue warp --------------------------
@@ -621,11 +747,23 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
           *(volatile int*)&s_abort = 1;
         }
       }
-      float* rbuf = red + rb * (CW * kOut) + warp * kOut + lane;
+      if (FAST) {
+        // lanes t = 0 and t = 1 hold the two halves (groups 0..3 and 4..7 of every chunk) of rows g and g+8
+        float lo = acc[0][0][0] + acc[1][0][0], hi = acc[0][0][2] + acc[1][0][2];
+        lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+        hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+        float* rbuf = red + rb * (CW * kOut) + warp * kOut;
+        if (t == 0) {
+          *reinterpret_cast<float2*>(rbuf + g * NCP) = make_float2(lo, 0.f);
+          *reinterpret_cast<float2*>(rbuf + (g + 8) * NCP) = make_float2(hi, 0.f);
+        }
+      } else {
+        float* rbuf = red + rb * (CW * kOut) + warp * kOut + lane;
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) rbuf[(mt * 4 + i) * 32] = acc[0][mt][i] + acc[1][mt][i];
+          for (int i = 0; i < 4; ++i) rbuf[(mt * 4 + i) * 32] = acc[0][mt][i] + acc[1][mt][i];
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&red_full[rb]);   // release: the stores above are visible to the waiter
       rb = rb + 1 == nred ? 0 : rb + 1;
@@ -683,14 +821,15 @@ struct Prologue {
   float eps = 0.f;
 };
 
-template <int NC, int CW, int CH, int PRO>
+template <int NC, int CW, int CH, int PRO, bool FAST>
 int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int M, int N, int K,
                 cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   constexpr int MT = (NC + 7) / 8;
-  constexpr int kOut = MT * 128;
+  constexpr int kOut = FAST ? kRows * 2 : MT * 128;
   constexpr int KC = 256 * CH;
   constexpr int kStageBytes = CH * kRows * (128 + 16);
   constexpr int kThreads = (CW + 2) * 32;
+  using XL = XLayout<NC>;
   PipeParams p;
   {
     const uint64_t wd[3] = {32, (uint64_t)N, (uint64_t)(K / 256)};
@@ -711,30 +850,55 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   p.ntiles = (N + kRows - 1) / kRows;
   const int kpad = ((K + KC - 1) / KC) * KC;
   const int stages_per_tile = kpad / KC;
-  int stages = (int)options().gemv_stages;
-  // Registers are the second buffer (a stage is handed back as soon as it has been copied out) and
-  // two CTAs share an SM, so one stage per CTA measured fastest; deeper rings only cost shared memory.
-  if (stages <= 0) stages = 1;
-  (void)stages_per_tile;
-  if (stages > kMaxStages) stages = kMaxStages;
   const size_t kMaxSmem = 227 * 1024;
   const int sms = sm_count();
-  auto kern = q4f16_gemv_pipe_kernel<NC, CW, CH, PRO>;
+  auto kern = q4f16_gemv_pipe_kernel<NC, CW, CH, PRO, FAST>;
   // Ask for the largest shared-memory carve-out: the default picks the smallest that fits ONE CTA,
   // which would keep further CTAs (or the next dependent launch) off the SM.
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  int max_per_sm = (int)options().gemv_ctas_per_sm;
-  if (max_per_sm <= 0) max_per_sm = 2;
+  auto fixed_bytes = [&](int stages) {
+    return (size_t)1024 /* base alignment slack */ + (4 * kMaxStages + 2) * sizeof(uint64_t) + (size_t)stages * kStageBytes +
+           (size_t)(stages + 1) * CW * kOut * sizeof(float);
+  };
+  auto block_bytes = [&](int k) { return XL::bytes(k) + (FAST ? (size_t)(k / 256) * 32 * sizeof(float) : 0); };
   size_t need = 0;
-  int kblk = 0, grid = 0;
-  // Prefer the whole of x beside the ring; give up ring depth before cutting K into blocks (a
-  // shallower ring costs little, K blocks cost a carry array and restaging).
-  for (;; --stages) {
-    const size_t fixed = 1024 /* base alignment slack */ + (4 * kMaxStages + 2) * sizeof(uint64_t) +
-                         (size_t)stages * kStageBytes + (size_t)(stages + 1) * CW * kOut * sizeof(float);
-    need = fixed + XLayout<NC>::bytes(kpad);
-    kblk = kpad;
-    if (need <= kMaxSmem) {
+  int kblk = kpad, grid = 0, stages = (int)options().gemv_stages;
+  bool placed = false;
+  if (FAST) {
+    // Two CTAs per SM, one stage each (registers are the second buffer, as in the exact form): measured fastest
+    // for every shape of the 7B decode step.  Deeper rings (up to a CTA's whole share of W resident, one CTA per
+    // SM so that the next launch's CTAs prefetch beside this launch's) were measured too: no faster for
+    // N = K = 4096 and 10-20 % slower for the large matmuls.  Options gemv.ctas_per_sm and gemv.stages
+    // still select them.
+    int per_sm = (int)options().gemv_ctas_per_sm;
+    if (per_sm <= 0) per_sm = 2;
+    if (per_sm > 2) per_sm = 2;
+    grid = sms * per_sm;
+    if (grid > p.ntiles) grid = p.ntiles;
+    p.tiles_per_cta = (p.ntiles + grid - 1) / grid;
+    // (an explicit stage count may use up to half an SM, so that two CTAs still fit)
+    const size_t budget = stages > 0 ? (228 * 1024 - 2 * 1024) / 2 : 76 * 1024;
+    int want = stages > 0 ? stages : p.tiles_per_cta * stages_per_tile;
+    if (want > kMaxStages) want = kMaxStages;
+    for (int st = want; st >= 1 && !placed; --st) {
+      need = fixed_bytes(st) + block_bytes(kpad);
+      if (need <= budget || (st == 1 && need <= kMaxSmem)) {
+        stages = st;
+        placed = true;
+      }
+    }
+  } else {
+    // Registers are the second buffer (a stage is handed back as soon as it has been copied out) and
+    // two CTAs share an SM, so one stage per CTA measured fastest; deeper rings only cost shared memory.
+    if (stages <= 0) stages = 1;
+    if (stages > kMaxStages) stages = kMaxStages;
+    int max_per_sm = (int)options().gemv_ctas_per_sm;
+    if (max_per_sm <= 0) max_per_sm = 2;
+    // Prefer the whole of x beside the ring; give up ring depth before cutting K into blocks (a
+    // shallower ring costs little, K blocks cost a carry array and restaging).
+    for (; stages >= 1 && !placed; --stages) {
+      need = fixed_bytes(stages) + block_bytes(kpad);
+      if (need > kMaxSmem) continue;
       // resident CTAs per SM as the hardware will place them (registers and threads count too);
       // the answer for the last shared-memory size is remembered (per thread, per kernel variant)
       static thread_local size_t cached_need = 0;
@@ -752,19 +916,28 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
       grid = sms * per_sm;
       if (grid > p.ntiles) grid = p.ntiles;
       p.tiles_per_cta = (p.ntiles + grid - 1) / grid;
+      placed = true;
       break;
     }
-    if (stages > 1) continue;
+  }
+  if (!placed) {
     // ... otherwise cut K into blocks of as many stages' worth as fit, leaving room for the carries.
+    stages = 1;
     grid = sms < p.ntiles ? sms : p.ntiles;
     p.tiles_per_cta = (p.ntiles + grid - 1) / grid;
     const size_t carries = (size_t)p.tiles_per_cta * kOut * sizeof(float);
-    if (fixed + carries + XLayout<NC>::bytes(KC) > kMaxSmem) return B200_ENOTREADY;   // caller falls back
-    kblk = (int)((kMaxSmem - fixed - carries) / XLayout<NC>::bytes(KC)) * KC;
-    need = fixed + carries + XLayout<NC>::bytes(kblk);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
-    if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemv: cudaFuncSetAttribute(%zu): %s", need, cudaGetErrorString(e));
-    break;
+    const size_t fixed = fixed_bytes(1);
+    if (fixed + carries + block_bytes(KC) > kMaxSmem) return B200_ENOTREADY;   // caller falls back
+    kblk = (int)((kMaxSmem - fixed - carries) / block_bytes(KC)) * KC;
+    need = fixed + carries + block_bytes(kblk);
+  }
+  {
+    static thread_local size_t attr_need = 0;      // (per thread, per kernel variant)
+    if (attr_need != need) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+      if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemv: cudaFuncSetAttribute(%zu): %s", need, cudaGetErrorString(e));
+      attr_need = need;
+    }
   }
   p.nstages = stages;
   p.kblk = kblk;
@@ -789,20 +962,30 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
 template <int CW, int CH, int PRO>
 int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int m, int n, int k,
                   cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
-  if (m == 1) return launch_pipe<1, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
-  if (m == 2) return launch_pipe<2, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
-  if (m <= 4) return launch_pipe<4, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
-  if (m <= 8) return launch_pipe<8, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
-  return launch_pipe<16, CW, CH, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m == 1) {
+    // batch 1: the fast form unless the caller asks for the reference's rounding of every weight
+    if (!options().gemv_exact) return launch_pipe<1, CW, CH, PRO, true>(x, wq, scales, y, m, n, k, stream, pro, red);
+    return launch_pipe<1, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);
+  }
+  if (m == 2) return launch_pipe<2, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m <= 4) return launch_pipe<4, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (m <= 8) return launch_pipe<8, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);
+  return launch_pipe<16, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);
+}
+
+template <int PRO>
+int dispatch_form(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int m, int n, int k,
+                  cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
+  return launch_pipe_m<8, 16, PRO>(x, wq, scales, y, m, n, k, stream, pro, red);
 }
 
 int dispatch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N, int64_t K,
                   cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   if (K % 256 != 0 || (reinterpret_cast<uintptr_t>(scales) & 15u)) return B200_ENOTREADY;
   int m = (int)M, n = (int)N, k = (int)K;
-  if (pro.kind == kPrologueRmsNorm) return launch_pipe_m<8, 16, kPrologueRmsNorm>(x, wq, scales, y, m, n, k, stream, pro, red);
-  if (pro.kind == kPrologueSwiGLU) return launch_pipe_m<8, 16, kPrologueSwiGLU>(x, wq, scales, y, m, n, k, stream, pro, red);
-  return launch_pipe_m<8, 16, kPrologueNone>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (pro.kind == kPrologueRmsNorm) return dispatch_form<kPrologueRmsNorm>(x, wq, scales, y, m, n, k, stream, pro, red);
+  if (pro.kind == kPrologueSwiGLU) return dispatch_form<kPrologueSwiGLU>(x, wq, scales, y, m, n, k, stream, pro, red);
+  return dispatch_form<kPrologueNone>(x, wq, scales, y, m, n, k, stream, pro, red);
 }
 
 PeerReduce make_reduce(const B200PeerReduce* r) {

@@ -19,6 +19,7 @@ struct Options {
   int64_t gemv_stages = 0;    // 0 = auto (bulk-copy pipeline depth)
   int64_t gemv_pdl = 1;       // programmatic dependent launch on the streaming kernels
   int64_t gemv_ctas_per_sm = 0;  // 0 = auto: cap on resident CTAs per SM used to size the grid
+  int64_t gemv_exact = 0;     // 1 = round every weight to fp16 as the reference does (the slower exact form of the skinny kernel)
   int64_t gemv_peer_wait_ms = 2000;  // how long the fused sum over ranks waits for the other GPUs' flags
   int64_t gemm_max_ctas = 0;  // 0 = one per SM; smaller values force several tiles per CTA (tests)
   int64_t gemm_ws_ksplit = 0; // 0 = auto: K slices (= cluster size) of the weight-stationary kernel

@@ -28,3 +28,14 @@ def cuda_lib():
 
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
     return _lib.lib()
+
+
+@pytest.fixture(params=["fast", "exact"])
+def gemv_form(request, cuda_lib):
+    """Runs a test under both arithmetic forms of the skinny kernel: the default one (group scale applied to
+    fp32 group sums) and the exact one (every weight rounded to fp16 first, option gemv.exact)."""
+    from relax_b200 import _lib
+
+    _lib.set_option("gemv.exact", 1 if request.param == "exact" else 0)
+    yield request.param
+    _lib.set_option("gemv.exact", 0)

@@ -303,7 +303,7 @@ def test_merged_chain_and_symbolic_batch_on_the_gpu():
 
     import oracle
     from relax_b200 import synth
-    from util import assert_matmul_close
+    from util import assert_matmul_close, skinny_form_is_unrounded, unrounded_slack
 
     M, K, N1, N2 = 5, 512, 256, 128
     x, wq1, s1 = synth.make_case(M, N1, K, seed=21)
@@ -317,6 +317,8 @@ def test_merged_chain_and_symbolic_batch_on_the_gpu():
     ref = oracle.c_matmul(h, wq2, s2).astype(np.float32)
     w2 = oracle.c_dequantize(wq2, s2).astype(np.float32)
     slack = 2.0 ** -10 * (np.abs(h.astype(np.float32)) @ np.abs(w2).T)
+    if skinny_form_is_unrounded(M):
+        slack = slack + 20 * unrounded_slack(h, w2)
     err = np.abs(y.numpy().astype(np.float32) - ref)
     assert (err <= 2.0 ** -9 * np.abs(ref) + 0.05 * slack + 1e-4).all(), err.max()
     # one executable, two batch sizes

@@ -168,9 +168,9 @@ def oracle_steps(cfg, layers, embed, final_norm, lm_head, tokens, steps, max_ctx
 # M = 1 with K <= 4096 takes the one-pass form of the RMSNorm prologue (row kept in registers)
 @pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (1, 4096, 4096), (1, 272, 2304), (1, 128, 8192), (3, 300, 4096), (16, 64, 256),
                                    (8, 4096, 2816)])
-def test_gemv_with_fused_neighbours(cuda_lib, M, N, K):
+def test_gemv_with_fused_neighbours(cuda_lib, M, N, K, gemv_form):
     from relax_b200 import synth
-    from util import assert_matmul_close
+    from util import assert_matmul_close, skinny_form_is_unrounded, unrounded_slack
 
     rng = np.random.default_rng(M * N + K)
     _, wq, s = synth.make_case(1, N, K, seed=K + M)
@@ -194,6 +194,8 @@ def test_gemv_with_fused_neighbours(cuda_lib, M, N, K):
         ref = oracle.c_matmul(a, wq, s).astype(np.float32)
         wd = oracle.c_dequantize(wq, s).astype(np.float32)
         slack = 2.0 ** -10 * (np.abs(a.astype(np.float32)) @ np.abs(wd).T)
+        if skinny_form_is_unrounded(M):
+            slack = slack + 20 * unrounded_slack(a, wd)
         err = np.abs(y.cpu().numpy().astype(np.float32) - ref)
         assert (err <= 2.0 ** -9 * np.abs(ref) + 0.05 * slack + 1e-4).all(), f"gemv_rmsnorm: max err {err.max()}"
     # aliasing x_out with x is refused
@@ -208,6 +210,8 @@ def test_gemv_with_fused_neighbours(cuda_lib, M, N, K):
     ref = oracle.c_matmul(a, wq, s).astype(np.float32)
     wd = oracle.c_dequantize(wq, s).astype(np.float32)
     slack = 2.0 ** -10 * (np.abs(a.astype(np.float32)) @ np.abs(wd).T)
+    if skinny_form_is_unrounded(M):
+        slack = slack + 20 * unrounded_slack(a, wd)
     err = np.abs(y.cpu().numpy().astype(np.float32) - ref)
     assert (err <= 2.0 ** -9 * np.abs(ref) + 0.05 * slack + 1e-4).all(), f"gemv_swiglu: max err {err.max()}"
     assert cuda_lib.b200_device_error_flags() == 0

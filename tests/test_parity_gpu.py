@@ -65,14 +65,14 @@ def run_matmul(x, wq, s, family="auto"):
     return out.cpu().numpy()
 
 
-def test_gemv_golden(cuda_lib, golden):
+def test_gemv_golden(cuda_lib, golden, gemv_form):
     for name, x, wq, s, w, y in golden_cases(golden):
         out = run_matmul(x, wq, s)
         assert_matmul_close(out, x, wq, s, name, y_ref=y)
 
 
 @pytest.mark.parametrize("m", list(range(1, 17)))
-def test_gemv_every_m(cuda_lib, m):
+def test_gemv_every_m(cuda_lib, m, gemv_form):
     x, wq, s = synth.make_case(m, 300, 1024, seed=m)
     assert_matmul_close(run_matmul(x, wq, s), x, wq, s, f"M={m}")
 
@@ -80,12 +80,12 @@ def test_gemv_every_m(cuda_lib, m):
 @pytest.mark.parametrize("n,k", [(1, 32), (15, 32), (16, 64), (17, 96), (33, 224), (100, 256), (129, 288),
                                  (4096, 4096), (11008, 4096), (4096, 11008), (1280, 8192), (1024, 1376)])
 @pytest.mark.parametrize("m", [1, 3, 8, 16])
-def test_gemv_shapes(cuda_lib, m, n, k):
+def test_gemv_shapes(cuda_lib, m, n, k, gemv_form):
     x, wq, s = synth.make_case(m, n, k, seed=7 * n + k + m)
     assert_matmul_close(run_matmul(x, wq, s), x, wq, s, f"M={m} N={n} K={k}")
 
 
-def test_gemv_known_answers(cuda_lib):
+def test_gemv_known_answers(cuda_lib, gemv_form):
     k, n = 256, 48
     rng = np.random.default_rng(5)
     s = rng.uniform(0.005, 0.02, (n, k // 32)).astype(np.float16)
@@ -108,7 +108,7 @@ def test_gemv_known_answers(cuda_lib):
 @pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (1, 100, 256), (2, 37, 1280), (4, 4096, 11008), (7, 333, 2304),
                                    (8, 2000, 11008), (13, 500, 4096), (16, 4096, 4096), (16, 1280, 8192),
                                    (16, 700, 11008), (16, 20000, 2048)])
-def test_gemv_both_kernels(cuda_lib, variant, m, n, k):
+def test_gemv_both_kernels(cuda_lib, variant, m, n, k, gemv_form):
     x, wq, s = synth.make_case(m, n, k, seed=n + k + m)
     try:
         relax_b200.set_option("gemv.variant", variant)
@@ -120,7 +120,7 @@ def test_gemv_both_kernels(cuda_lib, variant, m, n, k):
 
 
 @pytest.mark.parametrize("stages", [2, 3, 8, 16])
-def test_gemv_pipeline_depths(cuda_lib, stages):
+def test_gemv_pipeline_depths(cuda_lib, stages, gemv_form):
     x, wq, s = synth.make_case(3, 5000, 4096, seed=stages)
     try:
         relax_b200.set_option("gemv.stages", stages)
@@ -131,7 +131,7 @@ def test_gemv_pipeline_depths(cuda_lib, stages):
     assert cuda_lib.b200_device_error_flags() == 0
 
 
-def test_gemv_back_to_back_dependent_launches(cuda_lib):
+def test_gemv_back_to_back_dependent_launches(cuda_lib, gemv_form):
     # a chain y1 = W1 x, y2 = W2 y1, ... launched back to back: each launch may start (and
     # prefetch its weights) before the previous one has finished, but must not read x early
     n = k = 1024
