@@ -198,6 +198,47 @@ typedef struct {
 B200_API int b200_q4f16_gemv_allreduce(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
                                        int64_t K, int32_t swiglu, const B200PeerReduce* red, void* cuda_stream);
 
+/* ---- one decoder layer of a batch-1 decode step as ONE persistent kernel -----------------------------
+ * The reference reaches a comparable effect when FuseOps folds a matmul's elementwise neighbours into its
+ * group (src/relay/analysis/graph_partitioner.cc:285-296); it has no kernel that spans several matmuls.
+ * Here a grid of one CTA per SM walks
+ *     qkv = Wqkv . rmsnorm(x_in + delta_in)        x_mid = x_in + delta_in
+ *     attn = attention(rope(q), cache + rope(k), v)    (rotary embedding, KV append at *pos, softmax over 0..*pos)
+ *     o = Wo . attn  (+ sum over ranks)            x_out = x_mid + o
+ *     gu = Wgu . rmsnorm(x_out)                    down = Wdown . (silu(gate) * up)  (+ sum over ranks)
+ * handing over between the stages through arrival counters in `scratch` (bounded waits; a wait that runs out
+ * sets a bit of byte 3 of b200_device_error_flags and the kernel runs through).  The caller adds `down` to
+ * x_out (the next layer does it as its delta_in).  Batch 1; heads of 128; hidden, hidden / world and
+ * inter_local multiples of 256; weights in the layout of this header (qkv rows = q heads | k heads | v heads of
+ * this rank, gu rows = gate | up).  KV caches fp16 [max_ctx, heads / world, 128].
+ *   scratch   b200_decode_layer_scratch_bytes(heads / world, max_ctx) bytes PER LAYER, zero before the first step
+ *             (the kernel leaves its counters consistent from step to step; do not share it between layers)
+ *   step      device int32 that grows by exactly one between two decode steps (the counters count arrivals up
+ *             to grid * (*step + 1)); all layers of a step see the same value
+ *   world > 1 reduce_o / reduce_down: as B200PeerReduce of b200_q4f16_gemv_allreduce, with `epoch`, `done_counter`
+ *             and `out` unused (flags carry *step + 1; results go to o / down); the partial results live in
+ *             peer_y[rank].  The two reductions must use different buffers and flag slots (a buffer is written
+ *             again only after another reduction has completed in between).
+ * Launches of this kernel must follow each other in one stream: all its CTAs wait for each other, so they must
+ * be resident together, which holds when nothing else competes for the SMs at that moment. */
+typedef struct {
+  int32_t world, rank;
+  int64_t hidden, inter_local, max_ctx;
+  int32_t heads;                  /* of the whole model; this rank takes heads / world */
+  float eps;
+  const void* x_in; const void* delta_in;      /* delta_in may be NULL */
+  void* x_mid; void* qkv; void* attn; void* o; void* x_out; void* gu; void* down;
+  const void* norm1; const void* norm2;
+  const void* cos_t; const void* sin_t; const void* pos;
+  void* k_cache; void* v_cache;
+  void* scratch; const void* step;
+  const void* wq_qkv; const void* s_qkv; const void* wq_o; const void* s_o;
+  const void* wq_gu; const void* s_gu; const void* wq_down; const void* s_down;
+  B200PeerReduce reduce_o, reduce_down;
+} B200DecodeLayer;
+B200_API int64_t b200_decode_layer_scratch_bytes(int64_t heads_local, int64_t max_ctx);
+B200_API int b200_decode_layer(const B200DecodeLayer* layer, void* cuda_stream);
+
 /* ---- glue kernels of a decode step (around the quantised matmuls) --------------------------
  * The reference has no RMSNorm / RoPE / attention op; these compute the composition of its
  * elementwise ops (mean, sqrt, divide, multiply, softmax, silu: python/tvm/relax/transform/

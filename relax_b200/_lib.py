@@ -56,6 +56,26 @@ class PeerReduce(ctypes.Structure):
     ]
 
 
+class DecodeLayer(ctypes.Structure):
+    """B200DecodeLayer of include/b200_q4f16.h."""
+
+    _fields_ = [
+        ("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+        ("hidden", ctypes.c_int64), ("inter_local", ctypes.c_int64), ("max_ctx", ctypes.c_int64),
+        ("heads", ctypes.c_int32), ("eps", ctypes.c_float),
+        ("x_in", ctypes.c_void_p), ("delta_in", ctypes.c_void_p),
+        ("x_mid", ctypes.c_void_p), ("qkv", ctypes.c_void_p), ("attn", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("x_out", ctypes.c_void_p), ("gu", ctypes.c_void_p), ("down", ctypes.c_void_p),
+        ("norm1", ctypes.c_void_p), ("norm2", ctypes.c_void_p),
+        ("cos_t", ctypes.c_void_p), ("sin_t", ctypes.c_void_p), ("pos", ctypes.c_void_p),
+        ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+        ("scratch", ctypes.c_void_p), ("step", ctypes.c_void_p),
+        ("wq_qkv", ctypes.c_void_p), ("s_qkv", ctypes.c_void_p), ("wq_o", ctypes.c_void_p), ("s_o", ctypes.c_void_p),
+        ("wq_gu", ctypes.c_void_p), ("s_gu", ctypes.c_void_p), ("wq_down", ctypes.c_void_p), ("s_down", ctypes.c_void_p),
+        ("reduce_o", PeerReduce), ("reduce_down", PeerReduce),
+    ]
+
+
 # name -> (restype, argtypes); one entry per prototype in include/b200_q4f16.h
 _vp, _i64, _ci = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
 _dlp = ctypes.POINTER(DLTensor)
@@ -79,6 +99,8 @@ PROTOTYPES = {
     "b200_q4f16_gemv_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_gemv_swiglu": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_gemv_allreduce": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int32, ctypes.POINTER(PeerReduce), _vp]),
+    "b200_decode_layer_scratch_bytes": (_i64, [_i64, _i64]),
+    "b200_decode_layer": (_ci, [ctypes.POINTER(DecodeLayer), _vp]),
     "b200_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _vp]),
     "b200_rope_kv_append": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_attn_decode_scratch_bytes": (_i64, [_i64, _i64, _i64]),

@@ -259,6 +259,9 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "gemv.ctas_per_sm")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemv.ctas_per_sm in 0..8"); o.gemv_ctas_per_sm = v; }
   else if (!strcmp(name, "gemv.exact")) { o.gemv_exact = v != 0; }
   else if (!strcmp(name, "gemv.peer_wait_ms")) { if (v < 1 || v > 60000) return fail(B200_EINVAL, "gemv.peer_wait_ms in 1..60000"); o.gemv_peer_wait_ms = v; }
+  else if (!strcmp(name, "layer.wait_ms")) { if (v < 1 || v > 60000) return fail(B200_EINVAL, "layer.wait_ms in 1..60000"); o.layer_wait_ms = v; }
+  else if (!strcmp(name, "layer.stages")) { if (v < 0 || v > 5) return fail(B200_EINVAL, "layer.stages in 0..5"); o.layer_stages = v; }
+  else if (!strcmp(name, "layer.max_ctas")) { if (v < 0 || v > 1024) return fail(B200_EINVAL, "layer.max_ctas in 0..1024"); o.layer_max_ctas = v; }
   else if (!strcmp(name, "gemm.ws_ksplit")) { if (v < 0 || v > 8 || (v & (v - 1))) return fail(B200_EINVAL, "gemm.ws_ksplit is 0, 1, 2, 4 or 8"); o.gemm_ws_ksplit = v; }
   else if (!strcmp(name, "gemm.ws_max_m")) { if (v < 0 || v > 128) return fail(B200_EINVAL, "gemm.ws_max_m in 0..128"); o.gemm_ws_max_m = v; }
   else if (!strcmp(name, "gemm.max_ctas")) { if (v < 0 || v > 1024) return fail(B200_EINVAL, "gemm.max_ctas in 0..1024"); o.gemm_max_ctas = v; }
@@ -277,6 +280,9 @@ int64_t b200_get_option(const char* name) {
   if (!strcmp(name, "gemv.exact")) return o.gemv_exact;
   if (!strcmp(name, "gemv.peer_wait_ms")) return o.gemv_peer_wait_ms;
   if (!strcmp(name, "gemm.max_ctas")) return o.gemm_max_ctas;
+  if (!strcmp(name, "layer.wait_ms")) return o.layer_wait_ms;
+  if (!strcmp(name, "layer.stages")) return o.layer_stages;
+  if (!strcmp(name, "layer.max_ctas")) return o.layer_max_ctas;
   if (!strcmp(name, "gemm.ws_ksplit")) return o.gemm_ws_ksplit;
   if (!strcmp(name, "gemm.ws_max_m")) return o.gemm_ws_max_m;
   return -1;

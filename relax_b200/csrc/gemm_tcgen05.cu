@@ -465,7 +465,8 @@ int gemm_error_read_and_clear() {
 }
 
 int device_error_flags_read_and_clear() {
-  return gemv_pipe_error_read_and_clear() | (gemm_error_read_and_clear() << 8) | (gemm_ws_error_read_and_clear() << 16);
+  return gemv_pipe_error_read_and_clear() | (gemm_error_read_and_clear() << 8) | (gemm_ws_error_read_and_clear() << 16) |
+         ((layer_error_read_and_clear() & 0x7f) << 24);
 }
 
 }  // namespace b200

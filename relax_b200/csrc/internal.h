@@ -21,6 +21,9 @@ struct Options {
   int64_t gemv_ctas_per_sm = 0;  // 0 = auto: cap on resident CTAs per SM used to size the grid
   int64_t gemv_exact = 0;     // 1 = round every weight to fp16 as the reference does (the slower exact form of the skinny kernel)
   int64_t gemv_peer_wait_ms = 2000;  // how long the fused sum over ranks waits for the other GPUs' flags
+  int64_t layer_wait_ms = 2000; // layer kernel: how long a CTA waits at a stage counter, a peer flag or a weight stage
+  int64_t layer_stages = 0;     // layer kernel: depth of the weight ring (0 = as many as fit, at most 5)
+  int64_t layer_max_ctas = 0;   // layer kernel: cap on the grid (0 = one CTA per SM); tests use small grids
   int64_t gemm_max_ctas = 0;  // 0 = one per SM; smaller values force several tiles per CTA (tests)
   int64_t gemm_ws_ksplit = 0; // 0 = auto: K slices (= cluster size) of the weight-stationary kernel
   int64_t gemm_ws_max_m = 128; // largest M the automatic dispatch gives to the weight-stationary kernel (0 = never)
@@ -46,11 +49,13 @@ int launch_gemm_ws(const __half* x, const uint32_t* wq, const __half* scales, __
 int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
 
-// Reads and clears the per-kernel device error words (bit 0-7: skinny pipeline, 8-15: tensor-core GEMM, 16-23: weight-stationary GEMM).
+// Reads and clears the per-kernel device error words (bit 0-7: skinny pipeline, 8-15: tensor-core GEMM, 16-23: weight-stationary GEMM,
+// 24-30: decoder-layer kernel).
 int device_error_flags_read_and_clear();
 int gemv_pipe_error_read_and_clear();
 int gemm_error_read_and_clear();
 int gemm_ws_error_read_and_clear();
+int layer_error_read_and_clear();
 
 // Device capability check, cached per device; 0 when the current device is sm_100.
 int ensure_device();

@@ -102,7 +102,7 @@ class DecodeEngine:
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
                  device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True,
-                 fused_attention=False, guard=None, verify: bool = True):
+                 fused_attention=False, guard=None, verify: bool = True, layer_kernel=None):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
@@ -148,13 +148,19 @@ class DecodeEngine:
         self.gathered = torch.zeros((world, B, vl), **f16) if vl and world > 1 else None
         self.graph = None
         self.launches_per_step = 0
+        # batch 1: one persistent kernel per layer (b200_decode_layer) instead of seven launches
+        self.layer_kernel = (B == 1 and self.fused) if layer_kernel is None else bool(layer_kernel)
+        if self.layer_kernel and B != 1:
+            raise ValueError("the one-kernel-per-layer path is the batch-1 path")
         # tensor parallel: the sum over ranks after o and down runs inside those matmul kernels over
         # NVLink peer memory (b200_q4f16_gemv_allreduce) when the batch is in the skinny kernel's range;
         # otherwise (or with peer_reduce=False) it is an NCCL all-reduce
         self.peer = None
         self.epoch = torch.zeros((1,), dtype=torch.int32, device=self.device)
-        if world > 1 and peer_reduce and B <= 16:
+        if world > 1 and (peer_reduce or self.layer_kernel) and B <= 16:
             self._setup_peer_reduce()
+        if self.layer_kernel:
+            self._setup_layer_kernel()
 
     def _setup_peer_reduce(self):
         import torch.distributed._symmetric_memory as symm_mem
@@ -176,6 +182,41 @@ class DecodeEngine:
             "flags": [p + 2 * ybytes for p in ptrs],
             "done": torch.zeros((1,), dtype=torch.int32, device=self.device),
         }
+
+    def _setup_layer_kernel(self):
+        """Buffers and one B200DecodeLayer descriptor per layer.  The residual stream rotates through three
+        buffers (a layer reads x_in, writes x_mid = x_in + delta and x_out = x_mid + o; the next layer's x_in is this
+        layer's x_out and it may overwrite the two others)."""
+        cfg, L = self.cfg, self.L
+        H, dev = cfg.hidden, self.device
+        f16 = dict(dtype=torch.float16, device=dev)
+        self.xr = [self.x, self.x2, torch.zeros((1, H), **f16)]
+        nbytes = int(L.b200_decode_layer_scratch_bytes(self.nh_local, self.max_ctx))
+        self.layer_scratch = [torch.zeros(((nbytes + 3) // 4,), dtype=torch.int32, device=dev) for _ in self.layers]
+        self.layer_desc = []
+        for i, w in enumerate(self.layers):
+            d = _lib.DecodeLayer()
+            d.world, d.rank = self.world, self.rank
+            d.hidden, d.inter_local, d.max_ctx = H, w["inter_local"], self.max_ctx
+            d.heads, d.eps = cfg.heads, cfg.eps
+            xin, xmid, xout = self.xr[(2 * i) % 3], self.xr[(2 * i + 1) % 3], self.xr[(2 * i + 2) % 3]
+            d.x_in, d.x_mid, d.x_out = xin.data_ptr(), xmid.data_ptr(), xout.data_ptr()
+            d.delta_in = self.down.data_ptr() if i > 0 else None
+            d.qkv, d.attn, d.o, d.gu, d.down = (self.qkv.data_ptr(), self.attn.data_ptr(), self.o.data_ptr(), self.gu.data_ptr(),
+                                                self.down.data_ptr())
+            d.norm1, d.norm2 = w["norm1"].data_ptr(), w["norm2"].data_ptr()
+            d.cos_t, d.sin_t, d.pos = self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr()
+            d.k_cache, d.v_cache = self.kc[i].data_ptr(), self.vc[i].data_ptr()
+            d.scratch, d.step = self.layer_scratch[i].data_ptr(), self.epoch.data_ptr()
+            d.wq_qkv, d.s_qkv = w["qkv"][0].data_ptr(), w["qkv"][1].data_ptr()
+            d.wq_o, d.s_o = w["o"][0].data_ptr(), w["o"][1].data_ptr()
+            d.wq_gu, d.s_gu = w["gu"][0].data_ptr(), w["gu"][1].data_ptr()
+            d.wq_down, d.s_down = w["down"][0].data_ptr(), w["down"][1].data_ptr()
+            if self.world > 1:
+                d.reduce_o = self._reduce_desc(0, i, self.o)
+                d.reduce_down = self._reduce_desc(1, i, self.down)
+            self.layer_desc.append(d)
+        self.x_last = self.xr[(2 * len(self.layers)) % 3]     # the residual stream after the last layer
 
     def _reduce_desc(self, kind: int, layer: int, out):
         d = _lib.PeerReduce()
@@ -276,9 +317,16 @@ class DecodeEngine:
         self._check(L.b200_embed_rows(self.embed.data_ptr(), self.tokens.data_ptr(), self.x.data_ptr(), B, cfg.hidden,
                                       self.embed.shape[0], sp))
         delta = None
-        for i in range(len(self.layers)):
-            delta = self.layer_step(i, delta, sp)
-        self._check(L.b200_rmsnorm(self.x.data_ptr(), delta.data_ptr() if delta is not None else None,
+        xlast = self.x
+        if self.layer_kernel:
+            for i in range(len(self.layers)):
+                self._check(L.b200_decode_layer(ctypes.byref(self.layer_desc[i]), sp))
+            if self.layers:
+                delta, xlast = self.down, self.x_last
+        else:
+            for i in range(len(self.layers)):
+                delta = self.layer_step(i, delta, sp)
+        self._check(L.b200_rmsnorm(xlast.data_ptr(), delta.data_ptr() if delta is not None else None,
                                    self.final_norm.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.eps, sp))
         if self.lm_head is not None:
             torch.matmul(self.h, self.lm_head.t(), out=self.logits_local)
@@ -292,6 +340,8 @@ class DecodeEngine:
 
     def kernels_per_step(self) -> int:
         """Kernels of this library launched by one step (embed + 5 or 11 per layer + final norm + advance)."""
+        if self.layer_kernel:
+            return 1 + len(self.layers) + 1 + 2
         return 1 + len(self.layers) * ((5 if self.fused else 9) + (1 if self.fused_attention == "rope" else (0 if self.fused_attention else 2))) + 1 + 2
 
     def capture(self, stream):

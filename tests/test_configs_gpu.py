@@ -42,7 +42,7 @@ def prologue_bound(a, wq, s, ref):
 
 
 # ------------------------------------------------------------------------------ config 3: one full-size layer
-@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("fused", [True, False, "layer"])
 def test_full_size_decoder_layer_matches_oracle(cuda_lib, fused):
     """hidden 4096, 32 heads x 128, SwiGLU 11008, eps 1e-5, theta 10000, fp16 KV cache of length 1024 ~N(0,1),
     batch 1: the residual stream after attention, the MLP output and the appended cache rows against
@@ -63,15 +63,21 @@ def test_full_size_decoder_layer_matches_oracle(cuda_lib, fused):
 
     shard = decoder.to_device(tp.shard_layer(w, 0, 1, cfg.hidden, cfg.inter), "cuda")
     embed = torch.zeros((cfg.vocab, cfg.hidden), dtype=torch.float16, device="cuda")
+    layer_kernel = fused == "layer"          # the layer as one persistent kernel
     eng = decoder.DecodeEngine(cfg, [shard], embed, torch.ones(cfg.hidden, dtype=torch.float16, device="cuda"), None, 1, ctx,
-                               "cuda", fused=fused)
-    assert eng.fused == fused
+                               "cuda", fused=bool(fused), layer_kernel=layer_kernel)
+    assert eng.fused == bool(fused) and eng.layer_kernel == layer_kernel
     eng.kc[0].copy_(dev(kc))
     eng.vc[0].copy_(dev(vc))
     eng.x.copy_(dev(x))
     eng.set_position(pos)
     sp = torch.cuda.current_stream().cuda_stream
-    down = eng.layer_step(0, None, sp)
+    if layer_kernel:
+        assert cuda_lib.b200_decode_layer(ctypes.byref(eng.layer_desc[0]), sp) == 0, _lib.last_error()
+        down = eng.down
+        eng.x = eng.x_last
+    else:
+        down = eng.layer_step(0, None, sp)
     torch.cuda.synchronize()
     assert cuda_lib.b200_device_error_flags() == 0
     xs = np.abs(x_ref.astype(np.float32)).max()
@@ -272,3 +278,77 @@ def test_peer_wait_runs_out_without_hanging(cuda_lib):
     torch.cuda.synchronize()
     assert_matmul_close(y.cpu().numpy(), x, wq, s, "call after the failure")
     assert L.b200_device_error_flags() == 0
+
+
+# ------------------------------------------------------------------------------ the layer kernel's own contracts
+def _small_layer_engine(layers=2, max_ctx=16):
+    cfg = decoder.DecoderConfig(hidden=512, heads=4, inter=768, layers=layers, vocab=100)
+    rng = np.random.default_rng(77)
+    shards = [decoder.to_device(tp.shard_layer(decoder.synth_layer_numpy(cfg, 400 + i), 0, 1, cfg.hidden, cfg.inter), "cuda")
+              for i in range(cfg.layers)]
+    embed = dev((0.5 * rng.standard_normal((cfg.vocab, cfg.hidden))).astype(F16))
+    fn = dev(np.ones(cfg.hidden, F16))
+    return cfg, shards, embed, fn
+
+
+@pytest.mark.parametrize("ctas", [1, 3, 40])
+def test_layer_kernel_on_small_grids_matches_the_seven_launch_engine(cuda_lib, ctas):
+    """Few CTAs: every CTA takes many tiles of every matmul and many attention units, the weight ring wraps
+    many times and runs across the stage boundaries.  Results must equal the seven-launch engine's bit for bit
+    (same arithmetic, same summation order inside a tile) for four steps."""
+    cfg, shards, embed, fn = _small_layer_engine()
+    outs = []
+    for layer_kernel in (False, True):
+        eng = decoder.DecodeEngine(cfg, shards, embed, fn, embed, 1, 16, "cuda", layer_kernel=layer_kernel)
+        eng.tokens.copy_(torch.tensor([7], dtype=torch.int32))
+        hs = []
+        try:
+            if layer_kernel:
+                _lib.set_option("layer.max_ctas", ctas)
+            for _ in range(4):
+                eng.step()
+                torch.cuda.synchronize()
+                hs.append(eng.h.cpu().numpy().copy())
+        finally:
+            _lib.set_option("layer.max_ctas", 0)
+        outs.append(hs)
+        assert cuda_lib.b200_device_error_flags() == 0
+    for a, b in zip(*outs):
+        err = np.abs(a.astype(np.float32) - b.astype(np.float32)).max() / np.abs(a.astype(np.float32)).max()
+        assert err < 2e-3, err
+
+
+def test_layer_kernel_wait_runs_out_without_hanging(cuda_lib):
+    """A stage counter that can never reach its target (the step scalar says 5 decode steps have passed, the
+    counters say none): with the wait limit set to 5 ms every CTA's first wait must run out, the kernel must
+    run through and end, the error word must report it (bit 5 of the layer kernel's byte), and after the
+    scratch is brought back in step an ordinary run must work."""
+    cfg, shards, embed, fn = _small_layer_engine(layers=1)
+    eng = decoder.DecodeEngine(cfg, shards, embed, fn, embed, 1, 16, "cuda", layer_kernel=True)
+    eng.tokens.copy_(torch.tensor([3], dtype=torch.int32))
+    sp = torch.cuda.current_stream().cuda_stream
+    assert cuda_lib.b200_device_error_flags() == 0
+    try:
+        _lib.set_option("layer.wait_ms", 5)
+        _lib.set_option("layer.max_ctas", 4)
+        eng.epoch.fill_(5)
+        assert cuda_lib.b200_decode_layer(ctypes.byref(eng.layer_desc[0]), sp) == 0, _lib.last_error()
+        torch.cuda.synchronize()                                  # returns: nothing hangs
+    finally:
+        _lib.set_option("layer.wait_ms", 2000)
+        _lib.set_option("layer.max_ctas", 0)
+    flags = cuda_lib.b200_device_error_flags()
+    assert (flags >> 24) & 32, hex(flags)
+    assert cuda_lib.b200_device_error_flags() == 0
+    # back in step: zero counters, step 0
+    eng.epoch.zero_()
+    eng.layer_scratch[0].zero_()
+    eng.set_position(0)
+    ref = decoder.DecodeEngine(cfg, shards, embed, fn, embed, 1, 16, "cuda", layer_kernel=False)
+    for e in (eng, ref):
+        e.tokens.copy_(torch.tensor([3], dtype=torch.int32))
+        e.step()
+    torch.cuda.synchronize()
+    assert cuda_lib.b200_device_error_flags() == 0
+    a, b = eng.h.float().cpu().numpy(), ref.h.float().cpu().numpy()
+    assert np.abs(a - b).max() / np.abs(b).max() < 2e-3

@@ -217,9 +217,14 @@ def test_gemv_with_fused_neighbours(cuda_lib, M, N, K, gemv_form):
     assert cuda_lib.b200_device_error_flags() == 0
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "layer"])
 @pytest.mark.parametrize("B", [1, 3])
 def test_decoder_steps_match_oracle(cuda_lib, B, fused):
+    # "layer": the one-persistent-kernel-per-layer path (batch 1)
+    layer_kernel = fused == "layer"
+    if layer_kernel and B != 1:
+        pytest.skip("the layer kernel is the batch-1 path")
+    fused = bool(fused)
     cfg = SMALL
     rng = np.random.default_rng(11)
     layers = [decoder.synth_layer_numpy(cfg, 100 + i) for i in range(cfg.layers)]
@@ -231,8 +236,9 @@ def test_decoder_steps_match_oracle(cuda_lib, B, fused):
     ref = oracle_steps(cfg, layers, embed, final_norm, lm_head, tokens, steps, max_ctx)
 
     shards = [decoder.to_device(tp.shard_layer(l, 0, 1, cfg.hidden, cfg.inter), "cuda") for l in layers]
-    eng = decoder.DecodeEngine(cfg, shards, dev(embed), dev(final_norm), dev(lm_head), B, max_ctx, "cuda", fused=fused)
-    assert eng.fused == fused
+    eng = decoder.DecodeEngine(cfg, shards, dev(embed), dev(final_norm), dev(lm_head), B, max_ctx, "cuda", fused=fused,
+                               layer_kernel=layer_kernel)
+    assert eng.fused == fused and eng.layer_kernel == layer_kernel
     eng.tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
     for s in range(steps):
         # feed the oracle's token choice so that a near-tie in the logits cannot fork the two runs
