@@ -267,7 +267,8 @@ def run_decode(args, world, rank, dev, batches):
     for batch in batches:
         eng = decoder.DecodeEngine(cfg, layers, embed, final_norm, lm_head, batch, max_ctx, dev, rank, world,
                                    peer_reduce=not args.decode_nccl,
-                                   fused_attention="rope" if args.decode_attn2 else args.decode_attn1)
+                                   fused_attention="rope" if args.decode_attn2 else args.decode_attn1,
+                                   layer_kernel=(None if args.decode_layer_kernel < 0 else bool(args.decode_layer_kernel)))
         bp = min(batch, 4)                                            # sequences checked by the parity step
         ref = None
         if rank == 0 and not args.no_decode_parity:
@@ -373,7 +374,8 @@ def run_decode(args, world, rank, dev, batches):
                     "d2h_bytes_per_step": 4 * batch},
             "bytes_per_step_per_gpu": per_rank,
             "hbm_frac_of_measured": per_rank / (ms / steps * 1e-3) / 1e9 / measured_peaks()["hbm_gbs"],
-            "kernels_per_step": eng.kernels_per_step(), "engine": "fused prologues, skinny kernels" if eng.fused else
+            "kernels_per_step": eng.kernels_per_step(), "engine": "one persistent kernel per layer" if eng.layer_kernel else
+            "fused prologues, skinny kernels" if eng.fused else
             "separate RMSNorm/SwiGLU kernels, mid-batch tensor-core matmul",
             "lm_head": "fp16, tied to the embedding, vocabulary-sharded (library GEMM)",
             "allreduce": (None if world == 1 else "fused into the o/down matmul kernels over NVLink peer memory (fp16 partials, "
@@ -624,6 +626,8 @@ def main():
                     help="only the 7B-shaped decode measurement, as the line's own metric (for profiling the decode step)")
     ap.add_argument("--decode-attn1", action="store_true", help="rotary + attention + merge as one launch (measured slightly slower in a graph)")
     ap.add_argument("--decode-attn2", action="store_true", help="rotary + KV append inside the attention launch, merge as a second launch")
+    ap.add_argument("--decode-layer-kernel", type=int, default=-1,
+                    help="batch 1: 1 = one persistent kernel per layer, 0 = seven launches per layer, -1 = the engine's default")
     ap.add_argument("--decode-nccl", action="store_true", help="tensor-parallel sums through NCCL instead of the fused kernel")
     ap.add_argument("--decode-steps", type=int, default=32, help="timed tokens per sequence of the decode measurement")
     ap.add_argument("--decode-batches", type=lambda v: [int(x) for x in v.split(",")], default=[1, 16, 64],

@@ -205,7 +205,7 @@ B200_API int b200_q4f16_gemv_allreduce(const void* x, const void* wq, const void
  *     qkv = Wqkv . rmsnorm(x_in + delta_in)        x_mid = x_in + delta_in
  *     attn = attention(rope(q), cache + rope(k), v)    (rotary embedding, KV append at *pos, softmax over 0..*pos)
  *     o = Wo . attn  (+ sum over ranks)            x_out = x_mid + o
- *     gu = Wgu . rmsnorm(x_out)                    down = Wdown . (silu(gate) * up)  (+ sum over ranks)
+ *     act = silu(gate) * up,  gate | up = Wgu . rmsnorm(x_out)       down = Wdown . act  (+ sum over ranks)
  * handing over between the stages through arrival counters in `scratch` (bounded waits; a wait that runs out
  * sets a bit of byte 3 of b200_device_error_flags and the kernel runs through).  The caller adds `down` to
  * x_out (the next layer does it as its delta_in).  Batch 1; heads of 128; hidden, hidden / world and
@@ -227,7 +227,7 @@ typedef struct {
   int32_t heads;                  /* of the whole model; this rank takes heads / world */
   float eps;
   const void* x_in; const void* delta_in;      /* delta_in may be NULL */
-  void* x_mid; void* qkv; void* attn; void* o; void* x_out; void* gu; void* down;
+  void* x_mid; void* qkv; void* attn; void* o; void* x_out; void* act; void* down;   /* fp16: [hidden] [3*hidden/world] [hidden/world] [hidden] [hidden] [inter_local] [hidden] */
   const void* norm1; const void* norm2;
   const void* cos_t; const void* sin_t; const void* pos;
   void* k_cache; void* v_cache;

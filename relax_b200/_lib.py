@@ -65,7 +65,7 @@ class DecodeLayer(ctypes.Structure):
         ("heads", ctypes.c_int32), ("eps", ctypes.c_float),
         ("x_in", ctypes.c_void_p), ("delta_in", ctypes.c_void_p),
         ("x_mid", ctypes.c_void_p), ("qkv", ctypes.c_void_p), ("attn", ctypes.c_void_p), ("o", ctypes.c_void_p),
-        ("x_out", ctypes.c_void_p), ("gu", ctypes.c_void_p), ("down", ctypes.c_void_p),
+        ("x_out", ctypes.c_void_p), ("act", ctypes.c_void_p), ("down", ctypes.c_void_p),
         ("norm1", ctypes.c_void_p), ("norm2", ctypes.c_void_p),
         ("cos_t", ctypes.c_void_p), ("sin_t", ctypes.c_void_p), ("pos", ctypes.c_void_p),
         ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),

@@ -8,8 +8,8 @@
 //     1  qkv   = Wqkv . rmsnorm(x + delta)            (also writes x_mid = x + delta)
 //     2  attn  = attention(rope(q), cache + rope(k), v)  per (head, 128-token chunk), merged per head
 //     3  o     = Wo . attn                            (+ sum over tensor-parallel ranks)
-//     4  gu    = Wgu . rmsnorm(x_mid + o)             (also writes x_out = x_mid + o)
-//     5  down  = Wdown . (silu(gate) * up)            (+ sum over tensor-parallel ranks)
+//     4  act   = silu(gate) * up,  gate | up = Wgu . rmsnorm(x_mid + o)   (also writes x_out = x_mid + o)
+//     5  down  = Wdown . act                          (+ sum over tensor-parallel ranks)
 //
 // and the stages hand over through arrival counters in global memory (a grid barrier: every CTA adds
 // one when its stores are fenced, everyone polls until the count reaches grid * (step + 1); counters
@@ -18,8 +18,12 @@
 // so the next matmul's first tiles arrive while the current stage drains and during the attention.
 //
 // The four matmuls use the batch-1 fast form of the skinny kernel (gemv_pipe.cu): raw offset nibbles
-// into mma.sync, block-diagonal activations, group scales applied to fp32 group sums; RMSNorm, the
-// residual adds and SwiGLU run inside the staging of the activation vector.
+// into mma.sync, block-diagonal activations, group scales applied to fp32 group sums; RMSNorm and the
+// residual adds run inside the staging of the activation vector.  SwiGLU runs where the gate and up rows
+// are produced: a CTA takes the gate tile and the up tile of the same 16 outputs one after the other, and
+// its epilogue warp stores silu(gate) * up, so nobody has to recompute the 11008 activations per CTA.
+//
+// Warps: eight consumers (matmuls and attention), one TMA warp, one epilogue warp.
 //
 // Every wait is bounded by wall time: a wait that runs out sets a bit in the layer kernel's error word
 // (b200_device_error_flags), the CTA stops waiting and runs through, nothing hangs.
@@ -54,11 +58,15 @@ constexpr int kSBytes = CH * kRows * 16;
 constexpr int kStageBytes = kWBytes + kSBytes;
 constexpr int kMaxStages = 5;
 constexpr int kNumRed = 2;               // partial-sum buffers between the consumers and the epilogue warp
-constexpr int kThreads = (CW + 2) * 32;
+constexpr int kAttnHelpers = 0;           // extra warps that only work in the attention stage (8 were measured: the 18-warp CTA
+                                          // leaves 96 registers per thread, the matmuls spill and the layer gets 15 % slower)
+constexpr int kThreads = (CW + 2 + kAttnHelpers) * 32;
+constexpr int kAttnThreads = (CW + kAttnHelpers) * 32;
+constexpr int kAttnGroups = (CW + kAttnHelpers) / 4;
 constexpr int kConsumers = CW * 32;
 constexpr int kOut = kRows * 2;          // one value per row, padded to two
 constexpr int kAttnChunk = 128;
-constexpr int kTok = 16;                 // tokens per attention round and warp
+constexpr int kTok = 16;                 // tokens per attention round and warp (all loads of a round in flight together)
 constexpr uint64_t kProducerWaitNs = 30000000000ull;
 using XL = XLayout<1>;
 
@@ -80,7 +88,7 @@ struct LayerParams {
   __half* attn;                          // [nh * 128]
   __half* o;                             // [H]
   __half* x_out;                         // x_mid + o: the residual stream the next layer gets
-  __half* gu;                            // [2 * I]
+  __half* act;                           // [I]: silu(gate) * up
   __half* down;                          // [H]: the next layer's delta
   const __half* norm1;
   const __half* norm2;
@@ -118,6 +126,22 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Order in which a CTA takes the row tiles of a matmul.  Plain: cta, cta + grid, ...  Paired (gate | up): the
+// gate tile and the up tile of the same 16 outputs one after the other: pair p = cta, cta + grid, ... gives
+// tiles p and p + half.
+struct TileOrder {
+  int count;      // tiles this CTA takes
+  int cta, grid, half;
+  __device__ TileOrder(int N, bool paired, int cta_, int grid_) : cta(cta_), grid(grid_) {
+    const int ntiles = (N + kRows - 1) / kRows;
+    half = paired ? ntiles / 2 : 0;
+    const int units = paired ? half : ntiles;
+    const int mine = cta < units ? (units - cta + grid - 1) / grid : 0;
+    count = paired ? 2 * mine : mine;
+  }
+  __device__ int tile(int i) const { return half ? cta + (i >> 1) * grid + (i & 1) * half : cta + i * grid; }
+};
+
 __global__ void __launch_bounds__(kThreads, 1)
 q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
   extern __shared__ unsigned char smem_unaligned[];
@@ -134,8 +158,8 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
   __shared__ uint4 s_zero;
   __shared__ float s_part[CW];
   __shared__ float s_inv;
-  __shared__ float sm_m[2][4], sm_l[2][4], sm_acc[2][4][128];
-  __shared__ int s_last[2];
+  __shared__ float sm_m[4][4], sm_l[4][4], sm_acc[4][4][128];
+  __shared__ int s_last[4];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -171,6 +195,183 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
     }
   };
 
+  // Stage 2.  The attention warps in groups of four; a group takes (head, 128-token chunk) units.  Every lane has
+  // the K and V loads of 16 of its warp's tokens in flight at once.  The group that arrives last for a head merges
+  // that head's chunks.  `aw` = index among the attention warps.
+  auto attention_stage = [&](int aw) {
+    const int grp4 = aw >> 2;
+    const int wl = aw & 3;
+    const int gt = wl * 32 + lane;                 // thread within the group
+    const int pos = p.pos[0];
+    const int ctx = pos + 1;
+    const int used = (ctx + kAttnChunk - 1) / kAttnChunk;
+    const int nunits = p.nh * used;
+    const int nh = p.nh;
+    const int d0 = lane * 4;
+    const int r0 = d0 & 63;
+    const int64_t tok_stride = (int64_t)nh * 128;
+    // (the rotation angles only depend on the position: fetched before the wait)
+    const float4 cs = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)pos * 64 + r0);
+    const float4 sn = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)pos * 64 + r0);
+    const unsigned target = ((unsigned)*p.step + 1u) * (unsigned)grid;
+    if (aw == 0 && lane == 0) grid_wait(&p.bar[0], target);
+    bar_sync(2, kAttnThreads);
+    const float c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+    const float sign = lane < 16 ? -1.f : 1.f;
+    auto rotate = [&](const __half* v, float (&o)[4]) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(v + d0);
+      const __half2* hh = reinterpret_cast<const __half2*>(&raw);
+      const float2 a = __half22float2(hh[0]), e = __half22float2(hh[1]);
+      const float mine[4] = {a.x, a.y, e.x, e.y};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, mine[j], 16);
+        o[j] = __half2float(__float2half_rn(mine[j] * c[j] + sign * other * sv[j]));
+      }
+    };
+    for (int unit = (int)blockIdx.x * kAttnGroups + grp4; unit < nunits; unit += kAttnGroups * grid) {
+      const int h = unit / used, split = unit - h * used;
+      const int t0 = split * kAttnChunk;
+      const int t1 = min(ctx, t0 + kAttnChunk);
+      float* part = p.attn_scratch + ((int64_t)h * p.nsplit + split) * 130;
+      const __half* kb = p.k_cache + (int64_t)h * 128 + d0;
+      const __half* vb = p.v_cache + (int64_t)h * 128 + d0;
+      uint2 kv[kTok], vv[kTok];
+      auto load_round = [&](int tb) {
+#pragma unroll
+        for (int j = 0; j < kTok; ++j) {
+          const int tk = min(tb + j, t1 - 1);        // clamped: a token past the end is loaded but not used
+          kv[j] = *reinterpret_cast<const uint2*>(kb + tk * tok_stride);
+          vv[j] = *reinterpret_cast<const uint2*>(vb + tk * tok_stride);
+        }
+      };
+      const int tb0 = t0 + wl * kTok;
+      if (split == used - 1) {
+        if (wl == 0) {
+          // the new token belongs to this chunk: its rotated k and its v go into the caches first
+          float kr[4];
+          rotate(p.qkv + (nh + h) * 128, kr);
+          const int64_t slot = ((int64_t)pos * nh + h) * 128 + d0;
+          uint2 kw;
+          __half2* kh2 = reinterpret_cast<__half2*>(&kw);
+          kh2[0] = __floats2half2_rn(kr[0], kr[1]);
+          kh2[1] = __floats2half2_rn(kr[2], kr[3]);
+          *reinterpret_cast<uint2*>(p.k_cache + slot) = kw;
+          *reinterpret_cast<uint2*>(p.v_cache + slot) = *reinterpret_cast<const uint2*>(p.qkv + (2 * nh + h) * 128 + d0);
+        }
+        bar_sync(4 + grp4, 128);                   // the appended token is visible to the group
+      }
+      if (tb0 < t1) load_round(tb0);               // in flight while q is fetched and rotated
+      float qf[4];
+      rotate(p.qkv + h * 128, qf);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) qf[j] *= p.scale_log2e;
+      float m = -INFINITY, l = 0.f, av[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int tb = tb0; tb < t1; tb += 4 * kTok) {
+        if (tb != tb0) load_round(tb);
+        float sc[kTok];
+#pragma unroll
+        for (int j = 0; j < kTok; ++j) {
+          const __half2* kh = reinterpret_cast<const __half2*>(&kv[j]);
+          const float2 k01 = __half22float2(kh[0]), k23 = __half22float2(kh[1]);
+          sc[j] = qf[0] * k01.x + qf[1] * k01.y + qf[2] * k23.x + qf[3] * k23.y;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+          for (int j = 0; j < kTok; ++j) sc[j] += __shfl_xor_sync(0xffffffffu, sc[j], o);
+        float mn = m;
+#pragma unroll
+        for (int j = 0; j < kTok; ++j) {
+          if (tb + j >= t1) sc[j] = -INFINITY;
+          mn = fmaxf(mn, sc[j]);
+        }
+        const float corr = exp2f(m - mn);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) av[i] *= corr;
+#pragma unroll
+        for (int j = 0; j < kTok; ++j) {
+          const float pj = exp2f(sc[j] - mn);
+          const __half2* vh = reinterpret_cast<const __half2*>(&vv[j]);
+          const float2 v01 = __half22float2(vh[0]), v23 = __half22float2(vh[1]);
+          l += pj;
+          av[0] += pj * v01.x;
+          av[1] += pj * v01.y;
+          av[2] += pj * v23.x;
+          av[3] += pj * v23.y;
+        }
+        m = mn;
+      }
+      if (lane == 0) { sm_m[grp4][wl] = m; sm_l[grp4][wl] = l; }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sm_acc[grp4][wl][lane * 4 + j] = av[j];
+      bar_sync(4 + grp4, 128);
+      {
+        const float M = fmaxf(fmaxf(sm_m[grp4][0], sm_m[grp4][1]), fmaxf(sm_m[grp4][2], sm_m[grp4][3]));
+        float L = 0.f, A = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < 4; ++w2) {
+          const float f = (sm_m[grp4][w2] == -INFINITY) ? 0.f : exp2f(sm_m[grp4][w2] - M);
+          L += sm_l[grp4][w2] * f;
+          A += sm_acc[grp4][w2][gt] * f;
+        }
+        part[2 + gt] = A;
+        if (gt == 0) { part[0] = M; part[1] = L; }
+      }
+      // the group that arrives last for this head merges the chunks
+      __threadfence();
+      bar_sync(4 + grp4, 128);
+      if (gt == 0) s_last[grp4] = atomicAdd(&p.attn_counters[h], 1) == used - 1;
+      bar_sync(4 + grp4, 128);
+      if (s_last[grp4]) {
+        __threadfence();
+        if (gt == 0) p.attn_counters[h] = 0;
+        const float* pp = p.attn_scratch + (int64_t)h * p.nsplit * 130;
+        float M = -INFINITY, L = 0.f, A = 0.f;
+        for (int s0 = 0; s0 < used; s0 += 16) {
+          float Ms[16], Ls[16], As[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int si = min(s0 + j, used - 1);
+            Ms[j] = __ldcg(pp + si * 130);
+            Ls[j] = __ldcg(pp + si * 130 + 1);
+            As[j] = __ldcg(pp + si * 130 + 2 + gt);
+          }
+          float Mn = M;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (s0 + j < used) Mn = fmaxf(Mn, Ms[j]);
+          const float corr = exp2f(M - Mn);
+          L *= corr;
+          A *= corr;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (s0 + j < used) {
+              const float f = exp2f(Ms[j] - Mn);
+              L += Ls[j] * f;
+              A += As[j] * f;
+            }
+          }
+          M = Mn;
+        }
+        p.attn[h * 128 + gt] = __float2half_rn(A / L);
+      }
+      bar_sync(4 + grp4, 128);                     // sm_* and s_last are free for the next unit
+    }
+    // every attention warp of the CTA is through: the CTA signs off
+    __threadfence();
+    bar_sync(2, kAttnThreads);
+    if (aw == 0 && lane == 0) atom_add_release_gpu(&p.bar[1], 1u);
+  };
+
+  if (kAttnHelpers > 0 && warp >= CW + 2) {
+    // ------------------------------------------------------------------ attention helpers
+    pdl_wait();
+    attention_stage(warp - 2);
+    return;
+  }
+
   if (warp == CW) {
     // ------------------------------------------------------------------ producer warp
     // lane 0 streams the packed weights, lane 1 the scales of this CTA's tiles of the four matrices, in the
@@ -181,12 +382,13 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
       int s = 0;
       uint32_t round = 0;
       bool dead = false;
-      auto produce = [&](const CUtensorMap* tw, const CUtensorMap* ts, int N, int K) {
+      auto produce = [&](const CUtensorMap* tw, const CUtensorMap* ts, int N, int K, bool paired) {
         if (dead) return;
         prefetch_tmap(is_w ? tw : ts);
-        const int ntiles = (N + kRows - 1) / kRows;
+        const TileOrder order(N, paired, (int)blockIdx.x, grid);
         const int kpad = ((K + KC - 1) / KC) * KC;
-        for (int tile = blockIdx.x; tile < ntiles; tile += grid) {
+        for (int ti = 0; ti < order.count; ++ti) {
+          const int tile = order.tile(ti);
           for (int k0 = 0; k0 < kpad; k0 += KC, s = (s + 1 == p.nstages ? 0 : s + 1), round += (s == 0)) {
             if (round > 0) {
               if (*(volatile int*)&s_abort || !mbar_wait_ns_relaxed(&empty[s], (round - 1) & 1, kProducerWaitNs)) {
@@ -207,10 +409,10 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
           }
         }
       };
-      produce(&p.tm_w[0], &p.tm_s[0], p.N[0], p.K[0]);
-      produce(&p.tm_w[1], &p.tm_s[1], p.N[1], p.K[1]);
-      produce(&p.tm_w[2], &p.tm_s[2], p.N[2], p.K[2]);
-      produce(&p.tm_w[3], &p.tm_s[3], p.N[3], p.K[3]);
+      produce(&p.tm_w[0], &p.tm_s[0], p.N[0], p.K[0], false);
+      produce(&p.tm_w[1], &p.tm_s[1], p.N[1], p.K[1], false);
+      produce(&p.tm_w[2], &p.tm_s[2], p.N[2], p.K[2], true);
+      produce(&p.tm_w[3], &p.tm_s[3], p.N[3], p.K[3], false);
     }
     return;
   }
@@ -225,9 +427,13 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
     const unsigned target = step1 * (unsigned)grid;
     int rb = 0;
     uint32_t rround = 0;
-    auto finish = [&](int N, __half* y) {
-      const int ntiles = (N + kRows - 1) / kRows;
-      for (int tile = blockIdx.x; tile < ntiles; tile += grid) {
+    // paired: the tiles come as (gate, up) of the same 16 outputs; what is stored is silu(gate) * up, both rounded
+    // to fp16 first as the matmul's own output would be
+    auto finish = [&](int N, __half* y, bool paired) {
+      const TileOrder order(N, paired, (int)blockIdx.x, grid);
+      float gate = 0.f;
+      for (int ti = 0; ti < order.count; ++ti) {
+        const int tile = order.tile(ti);
         if (!mbar_try_wait(&red_full[rb], rround & 1)) {
           if (!*(volatile int*)&s_abort && !mbar_wait_ns_relaxed(&red_full[rb], rround & 1, kProducerWaitNs)) {
             atomicOr(&g_layer_error, 4);
@@ -239,7 +445,14 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
 #pragma unroll
         for (int w2 = 0; w2 < CW; ++w2) sum += rbuf[w2 * kOut + lane];
         const int row = tile * kRows + (lane >> 1);
-        if ((lane & 1) == 0 && row < N) y[row] = __float2half_rn(sum);
+        if (!paired) {
+          if ((lane & 1) == 0 && row < N) y[row] = __float2half_rn(sum);
+        } else if ((ti & 1) == 0) {
+          gate = __half2float(__float2half_rn(sum));
+        } else {
+          const float up = __half2float(__float2half_rn(sum));
+          if ((lane & 1) == 0) y[row - order.half * kRows] = __float2half_rn(gate / (1.f + __expf(-gate)) * up);
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&red_empty[rb]);
         rb = rb + 1 == kNumRed ? 0 : rb + 1;
@@ -306,22 +519,22 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
       }
     };
 
-    finish(p.N[0], p.qkv);
+    finish(p.N[0], p.qkv, false);
     sign_off(&p.bar[0]);
     if (p.peer_o.world > 1) {
-      finish(p.N[1], p.peer_o.y_local);
+      finish(p.N[1], p.peer_o.y_local, false);
       peer_sum(p.peer_o, &p.bar[4], p.N[1], p.o);
     } else {
-      finish(p.N[1], p.o);
+      finish(p.N[1], p.o, false);
     }
     sign_off(&p.bar[2]);
-    finish(p.N[2], p.gu);
+    finish(p.N[2], p.act, true);
     sign_off(&p.bar[3]);
     if (p.peer_down.world > 1) {
-      finish(p.N[3], p.peer_down.y_local);
+      finish(p.N[3], p.peer_down.y_local, false);
       peer_sum(p.peer_down, &p.bar[5], p.N[3], p.down);
     } else {
-      finish(p.N[3], p.down);
+      finish(p.N[3], p.down, false);
     }
     return;
   }
@@ -464,6 +677,63 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
     const int kpad = ((K + KC - 1) / KC) * KC;
     const int groups = kpad >> 5;
     float inv = 1.f;
+    if (kind == 1 && K <= kConsumers * 16) {
+      // a row of at most 2 * 8 * 256 values: a thread's two 8-value words are the same in the statistics pass and in
+      // the staging pass, so the three vectors are loaded once, all loads in flight together, and kept in registers
+      uint4 keep[2], nwv[2], dl[2];
+      bool live[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int k = (tid + r * kConsumers) * 8;
+        live[r] = k < K;
+        keep[r] = nwv[r] = dl[r] = make_uint4(0, 0, 0, 0);
+        if (live[r]) {
+          keep[r] = *reinterpret_cast<const uint4*>(src + k);
+          if (add) dl[r] = *reinterpret_cast<const uint4*>(add + k);
+          nwv[r] = *reinterpret_cast<const uint4*>(nw + k);
+        }
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        if (!live[r]) continue;
+        const int k = (tid + r * kConsumers) * 8;
+        if (add) keep[r] = add_f16x8(keep[r], dl[r]);
+        if (sum_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(sum_out + k) = keep[r];
+        const __half2* h = reinterpret_cast<const __half2*>(&keep[r]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) s_part[warp] = ss;
+      bar_sync(1, kConsumers);
+      float tot = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < CW; ++w2) tot += s_part[w2];
+      inv = rsqrtf(tot / (float)K + p.eps);
+      const int words = kpad >> 3;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int j = tid + r * kConsumers;
+        if (j >= words) continue;                // (words is a multiple of 32: whole warps leave together)
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (j * 8 < K) v = scale_f16x8(keep[r], inv, nwv[r]);
+        float psum = stage_word(j, v);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);       // a group's four words sit in four consecutive lanes
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        if ((j & 3) == 0) store_group_sum(j >> 2, psum);
+      }
+      // words beyond the two a thread holds (K < the padded length): zeros
+      for (int j = tid + 2 * kConsumers; j < words; j += kConsumers) {
+        float psum = stage_word(j, make_uint4(0, 0, 0, 0));
+        if ((j & 3) == 0) store_group_sum(j >> 2, psum);
+      }
+      bar_sync(1, kConsumers);
+      return;
+    }
     if (kind == 1) {
       float ss = 0.f;
       for (int k = tid * 8; k < K; k += kConsumers * 8) {
@@ -527,10 +797,10 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
   // This CTA's row tiles of one matmul; `have` says that the first stage is already in fw / fsc.
   uint4 fw[U][2][2];
   uint2 fsc[U][2];
-  auto gemv_tiles = [&](int N, int K, bool have) {
-    const int ntiles = (N + kRows - 1) / kRows;
+  auto gemv_tiles = [&](int N, int K, bool have, bool paired) {
+    const TileOrder order(N, paired, (int)blockIdx.x, grid);
     const int kpad = ((K + KC - 1) / KC) * KC;
-    for (int tile = blockIdx.x; tile < ntiles; tile += grid) {
+    for (int ti = 0; ti < order.count; ++ti) {
       acc0 = acc1 = acc2 = acc3 = 0.f;
       const uint4* xk = x_thr;
       const float4* ck = c_thr;
@@ -573,181 +843,25 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
   pdl_wait();
   const unsigned target = ((unsigned)*p.step + 1u) * (unsigned)grid;
   stage_x(1, p.x_in, p.delta_in, p.norm1, p.x_mid, p.K[0]);
-  gemv_tiles(p.N[0], p.K[0], pre);
+  gemv_tiles(p.N[0], p.K[0], pre, false);
 
   // ---- stage 2: rotary embedding, KV append, attention over the cache --------------------------------
-  wait_stage(&p.bar[0], target);
-  {
-    const int grp2 = warp >> 2;                    // two groups of four warps, each takes (head, chunk) units
-    const int wl = warp & 3;
-    const int gt = tid & 127;                      // thread within the group
-    const int pos = p.pos[0];
-    const int ctx = pos + 1;
-    const int used = (ctx + kAttnChunk - 1) / kAttnChunk;
-    const int nunits = p.nh * used;
-    const int nh = p.nh;
-    const int d0 = lane * 4;
-    const int r0 = d0 & 63;
-    const float4 cs = *reinterpret_cast<const float4*>(p.cos_t + (int64_t)pos * 64 + r0);
-    const float4 sn = *reinterpret_cast<const float4*>(p.sin_t + (int64_t)pos * 64 + r0);
-    const float c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-    const float sign = lane < 16 ? -1.f : 1.f;
-    auto rotate = [&](const __half* v, float (&o)[4]) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(v + d0);
-      const __half2* hh = reinterpret_cast<const __half2*>(&raw);
-      const float2 a = __half22float2(hh[0]), e = __half22float2(hh[1]);
-      const float mine[4] = {a.x, a.y, e.x, e.y};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float other = __shfl_xor_sync(0xffffffffu, mine[j], 16);
-        o[j] = __half2float(__float2half_rn(mine[j] * c[j] + sign * other * sv[j]));
-      }
-    };
-    const int64_t tok_stride = (int64_t)nh * 128;
-    for (int unit = (int)blockIdx.x * 2 + grp2; unit < nunits; unit += 2 * grid) {
-      const int h = unit / used, split = unit - h * used;
-      const int t0 = split * kAttnChunk;
-      const int t1 = min(ctx, t0 + kAttnChunk);
-      float* part = p.attn_scratch + ((int64_t)h * p.nsplit + split) * 130;
-      if (split == used - 1 && wl == 0) {
-        // the new token belongs to this chunk: its rotated k and its v go into the caches first
-        float kr[4];
-        rotate(p.qkv + (nh + h) * 128, kr);
-        const int64_t slot = ((int64_t)pos * nh + h) * 128 + d0;
-        uint2 kw;
-        __half2* kh2 = reinterpret_cast<__half2*>(&kw);
-        kh2[0] = __floats2half2_rn(kr[0], kr[1]);
-        kh2[1] = __floats2half2_rn(kr[2], kr[3]);
-        *reinterpret_cast<uint2*>(p.k_cache + slot) = kw;
-        *reinterpret_cast<uint2*>(p.v_cache + slot) = *reinterpret_cast<const uint2*>(p.qkv + (2 * nh + h) * 128 + d0);
-      }
-      float qf[4];
-      rotate(p.qkv + h * 128, qf);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) qf[j] *= p.scale_log2e;
-      bar_sync(4 + grp2, 128);                     // the appended token is visible to the group
-      float m = -INFINITY, l = 0.f, av[4] = {0.f, 0.f, 0.f, 0.f};
-      const __half* kb = p.k_cache + (int64_t)h * 128 + d0;
-      const __half* vb = p.v_cache + (int64_t)h * 128 + d0;
-      for (int tb = t0 + wl * kTok; tb < t1; tb += 4 * kTok) {
-        uint2 kv[kTok], vv[kTok];
-#pragma unroll
-        for (int j = 0; j < kTok; ++j) {
-          const int tk = min(tb + j, t1 - 1);
-          kv[j] = *reinterpret_cast<const uint2*>(kb + tk * tok_stride);
-          vv[j] = *reinterpret_cast<const uint2*>(vb + tk * tok_stride);
-        }
-        float sc[kTok];
-#pragma unroll
-        for (int j = 0; j < kTok; ++j) {
-          const __half2* kh = reinterpret_cast<const __half2*>(&kv[j]);
-          const float2 k01 = __half22float2(kh[0]), k23 = __half22float2(kh[1]);
-          sc[j] = qf[0] * k01.x + qf[1] * k01.y + qf[2] * k23.x + qf[3] * k23.y;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-          for (int j = 0; j < kTok; ++j) sc[j] += __shfl_xor_sync(0xffffffffu, sc[j], o);
-        float mn = m;
-#pragma unroll
-        for (int j = 0; j < kTok; ++j) {
-          if (tb + j >= t1) sc[j] = -INFINITY;
-          mn = fmaxf(mn, sc[j]);
-        }
-        const float corr = exp2f(m - mn);
-        l *= corr;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) av[i] *= corr;
-#pragma unroll
-        for (int j = 0; j < kTok; ++j) {
-          const float pj = exp2f(sc[j] - mn);
-          const __half2* vh = reinterpret_cast<const __half2*>(&vv[j]);
-          const float2 v01 = __half22float2(vh[0]), v23 = __half22float2(vh[1]);
-          l += pj;
-          av[0] += pj * v01.x;
-          av[1] += pj * v01.y;
-          av[2] += pj * v23.x;
-          av[3] += pj * v23.y;
-        }
-        m = mn;
-      }
-      if (lane == 0) { sm_m[grp2][wl] = m; sm_l[grp2][wl] = l; }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) sm_acc[grp2][wl][lane * 4 + j] = av[j];
-      bar_sync(4 + grp2, 128);
-      {
-        const float M = fmaxf(fmaxf(sm_m[grp2][0], sm_m[grp2][1]), fmaxf(sm_m[grp2][2], sm_m[grp2][3]));
-        float L = 0.f, A = 0.f;
-#pragma unroll
-        for (int w2 = 0; w2 < 4; ++w2) {
-          const float f = (sm_m[grp2][w2] == -INFINITY) ? 0.f : exp2f(sm_m[grp2][w2] - M);
-          L += sm_l[grp2][w2] * f;
-          A += sm_acc[grp2][w2][gt] * f;
-        }
-        part[2 + gt] = A;
-        if (gt == 0) { part[0] = M; part[1] = L; }
-      }
-      // the group that arrives last for this head merges the chunks
-      __threadfence();
-      bar_sync(4 + grp2, 128);
-      if (gt == 0) s_last[grp2] = atomicAdd(&p.attn_counters[h], 1) == used - 1;
-      bar_sync(4 + grp2, 128);
-      if (s_last[grp2]) {
-        __threadfence();
-        if (gt == 0) p.attn_counters[h] = 0;
-        const float* pp = p.attn_scratch + (int64_t)h * p.nsplit * 130;
-        float M = -INFINITY, L = 0.f, A = 0.f;
-        for (int s0 = 0; s0 < used; s0 += 16) {
-          float Ms[16], Ls[16], As[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int si = min(s0 + j, used - 1);
-            Ms[j] = __ldcg(pp + si * 130);
-            Ls[j] = __ldcg(pp + si * 130 + 1);
-            As[j] = __ldcg(pp + si * 130 + 2 + gt);
-          }
-          float Mn = M;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (s0 + j < used) Mn = fmaxf(Mn, Ms[j]);
-          const float corr = exp2f(M - Mn);
-          L *= corr;
-          A *= corr;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            if (s0 + j < used) {
-              const float f = exp2f(Ms[j] - Mn);
-              L += Ls[j] * f;
-              A += As[j] * f;
-            }
-          }
-          M = Mn;
-        }
-        p.attn[h * 128 + gt] = __float2half_rn(A / L);
-      }
-      bar_sync(4 + grp2, 128);                     // sm_* and s_last are free for the next unit
-    }
-  }
-  bar_sync(1, kConsumers);
-  if (tid == 0) {
-    __threadfence();
-    atom_add_release_gpu(&p.bar[1], 1u);
-  }
+  attention_stage(warp);
 
   // ---- stage 3: o projection ------------------------------------------------------------------------
   wait_stage(&p.bar[1], target);
   stage_x(0, p.attn, nullptr, nullptr, nullptr, p.K[1]);
-  gemv_tiles(p.N[1], p.K[1], false);
+  gemv_tiles(p.N[1], p.K[1], false, false);
 
   // ---- stage 4: gate | up -----------------------------------------------------------------------------
   wait_stage(&p.bar[2], target);
   stage_x(1, p.x_mid, p.o, p.norm2, p.x_out, p.K[2]);
-  gemv_tiles(p.N[2], p.K[2], false);
+  gemv_tiles(p.N[2], p.K[2], false, true);
 
   // ---- stage 5: down projection ------------------------------------------------------------------------
   wait_stage(&p.bar[3], target);
-  stage_x(2, p.gu, nullptr, nullptr, nullptr, p.K[3]);
-  gemv_tiles(p.N[3], p.K[3], false);
+  stage_x(0, p.act, nullptr, nullptr, nullptr, p.K[3]);
+  gemv_tiles(p.N[3], p.K[3], false, false);
 
   if (*(volatile int*)&s_abort) {
     const uint64_t t0 = globaltimer_ns();
@@ -819,12 +933,12 @@ int b200_decode_layer(const B200DecodeLayer* a, void* stream) {
   if (a->world < 1 || a->world > 8 || a->heads % a->world != 0 || a->hidden % (a->world * 256) != 0)
     return fail(B200_EINVAL, "%s: world %d does not divide %d heads / hidden %lld into whole 256-blocks", who, a->world, a->heads, (long long)a->hidden);
   if (a->hidden != (int64_t)a->heads * 128) return fail(B200_EINVAL, "%s: heads of 128 dimensions only (hidden = heads * 128)", who);
-  const void* need[] = {a->x_in, a->x_mid, a->qkv, a->attn, a->o, a->x_out, a->gu, a->down, a->norm1, a->norm2, a->cos_t, a->sin_t, a->pos,
+  const void* need[] = {a->x_in, a->x_mid, a->qkv, a->attn, a->o, a->x_out, a->act, a->down, a->norm1, a->norm2, a->cos_t, a->sin_t, a->pos,
                         a->k_cache, a->v_cache, a->scratch, a->step, a->wq_qkv, a->s_qkv, a->wq_o, a->s_o, a->wq_gu, a->s_gu, a->wq_down, a->s_down};
   for (const void* ptr : need)
     if (!ptr) return fail(B200_EINVAL, "%s: null pointer in the descriptor", who);
   for (const void* ptr : {a->x_in, (const void*)a->x_mid, (const void*)a->qkv, (const void*)a->attn, (const void*)a->o, (const void*)a->x_out,
-                          (const void*)a->gu, (const void*)a->down, a->norm1, a->norm2, a->delta_in})
+                          (const void*)a->act, (const void*)a->down, a->norm1, a->norm2, a->delta_in})
     if (reinterpret_cast<uintptr_t>(ptr) & 15u) return fail(B200_EINVAL, "%s: activation buffers must be 16-byte aligned", who);
   if (a->x_mid == a->x_in || a->x_out == a->x_mid) return fail(B200_EINVAL, "%s: x_mid must not alias x_in, nor x_out x_mid (other CTAs still read them)", who);
   int rc = ensure_device();
@@ -839,7 +953,7 @@ int b200_decode_layer(const B200DecodeLayer* a, void* stream) {
   if ((rc = fill_maps(p, 3, a->wq_down, a->s_down, H, il))) return rc;
   p.x_in = (const __half*)a->x_in; p.delta_in = (const __half*)a->delta_in; p.x_mid = (__half*)a->x_mid;
   p.qkv = (__half*)a->qkv; p.attn = (__half*)a->attn; p.o = (__half*)a->o; p.x_out = (__half*)a->x_out;
-  p.gu = (__half*)a->gu; p.down = (__half*)a->down;
+  p.act = (__half*)a->act; p.down = (__half*)a->down;
   p.norm1 = (const __half*)a->norm1; p.norm2 = (const __half*)a->norm2; p.eps = a->eps;
   p.cos_t = (const float*)a->cos_t; p.sin_t = (const float*)a->sin_t; p.pos = (const int*)a->pos;
   p.k_cache = (__half*)a->k_cache; p.v_cache = (__half*)a->v_cache;

@@ -202,8 +202,8 @@ class DecodeEngine:
             xin, xmid, xout = self.xr[(2 * i) % 3], self.xr[(2 * i + 1) % 3], self.xr[(2 * i + 2) % 3]
             d.x_in, d.x_mid, d.x_out = xin.data_ptr(), xmid.data_ptr(), xout.data_ptr()
             d.delta_in = self.down.data_ptr() if i > 0 else None
-            d.qkv, d.attn, d.o, d.gu, d.down = (self.qkv.data_ptr(), self.attn.data_ptr(), self.o.data_ptr(), self.gu.data_ptr(),
-                                                self.down.data_ptr())
+            d.qkv, d.attn, d.o, d.act, d.down = (self.qkv.data_ptr(), self.attn.data_ptr(), self.o.data_ptr(), self.act.data_ptr(),
+                                                 self.down.data_ptr())
             d.norm1, d.norm2 = w["norm1"].data_ptr(), w["norm2"].data_ptr()
             d.cos_t, d.sin_t, d.pos = self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr()
             d.k_cache, d.v_cache = self.kc[i].data_ptr(), self.vc[i].data_ptr()
