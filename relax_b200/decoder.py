@@ -148,8 +148,11 @@ class DecodeEngine:
         self.gathered = torch.zeros((world, B, vl), **f16) if vl and world > 1 else None
         self.graph = None
         self.launches_per_step = 0
-        # batch 1: one persistent kernel per layer (b200_decode_layer) instead of seven launches
-        self.layer_kernel = (B == 1 and self.fused) if layer_kernel is None else bool(layer_kernel)
+        # batch 1: one persistent kernel per layer (b200_decode_layer) instead of seven launches.  Off by default:
+        # measured on B200 at the 7B shape it is as fast as the seven launches on one GPU (1.94 against 1.90 ms per
+        # token) and slower on two (2.07 against 1.89), because every stage boundary inside it costs what a
+        # dependent launch costs, and its attention stage has only eight warps per SM with loads in flight
+        self.layer_kernel = False if layer_kernel is None else bool(layer_kernel)
         if self.layer_kernel and B != 1:
             raise ValueError("the one-kernel-per-layer path is the batch-1 path")
         # tensor parallel: the sum over ranks after o and down runs inside those matmul kernels over
