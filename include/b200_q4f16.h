@@ -137,8 +137,33 @@ B200_API int b200_q4f16_dequantize_dl(const B200DLTensor* wq, const B200DLTensor
 #define B200_FAMILY_AUTO 0
 #define B200_FAMILY_GEMV 1
 #define B200_FAMILY_GEMM 2
+/* `family` bits 0-7: B200_FAMILY_*; bits 8-15: 0 = the process-wide weight layout (option "weights.layout"),
+ * else B200_LAYOUT_* + 1 for this call (B200_FAMILY_WITH_LAYOUT). */
+#define B200_FAMILY_WITH_LAYOUT(family, layout) ((family) | (((layout) + 1) << 8))
 B200_API int b200_q4f16_matmul_dl_family(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales,
                                          B200DLTensor* y, int32_t family);
+
+/* ---- offline weight repack --------------------------------------------------------------
+ * The reference binds weights into the executable as constants when it builds
+ * (python/tvm/relax/vm.py:620-629 hands `const_name_to_constant` to the external codegen's modules), so a
+ * backend is free to store them in the order its kernels prefer.  B200_LAYOUT_REFERENCE is what the
+ * reference's encoder writes: nibble j of word i of a row is k = 8 i + j.  B200_LAYOUT_PAIRED keeps shape,
+ * dtype and scales and permutes the nibbles inside every 32-bit word to k0,k2,k4,k6,k1,k3,k5,k7: the kernels'
+ * mask-and-or unpack then yields (k0,k1)(k2,k3)(k4,k5)(k6,k7) directly, which saves the tensor-core kernels'
+ * dequantisers four byte permutes per word and the skinny kernels the permutation of x.
+ * repack: reference order -> `layout`; unpack: `layout` -> reference order; each is the other's exact
+ * inverse (bit for bit).  `out` may be the same buffer as `in` (in place) but must not otherwise overlap it.
+ * Every matmul and dequantise entry point reads its weights in the process-wide layout (option
+ * "weights.layout", default B200_LAYOUT_REFERENCE) unless the call names one (the *_layout entry points,
+ * B200_FAMILY_WITH_LAYOUT). */
+#define B200_LAYOUT_REFERENCE 0
+#define B200_LAYOUT_PAIRED 1
+B200_API int b200_q4f16_repack(const void* wq, void* packed_out, int64_t N, int64_t K, int32_t layout, void* stream);
+B200_API int b200_q4f16_unpack(const void* packed, void* wq_out, int64_t N, int64_t K, int32_t layout, void* stream);
+B200_API int b200_q4f16_matmul_layout(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
+                                      int64_t K, int32_t layout, void* stream);
+B200_API int b200_q4f16_dequantize_layout(const void* wq, const void* scales, void* w_out, int64_t N, int64_t K,
+                                          int32_t layout, void* stream);
 
 /* ---- packed-function symbols of the reference's C backend ABI ---------------------------
  * Signature TVMBackendPackedCFunc (include/tvm/runtime/c_backend_api.h:49-51); the form the

@@ -15,6 +15,8 @@ ships no vectors for this path and cannot be built here); see the header of
 from .q4f16 import (  # noqa: F401
     pack_nibbles,
     unpack_nibbles,
+    repack_paired,
+    unpack_paired,
     dequantize,
     matmul,
     matmul_acc32,

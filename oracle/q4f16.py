@@ -42,6 +42,25 @@ def unpack_nibbles(wq: np.ndarray) -> np.ndarray:
     return q.reshape(wq.shape[0], -1).astype(np.uint8)
 
 
+# Nibble position p of a word of the "paired" layout holds element k = PAIRED_ORDER[p] of the word's eight
+# (the library's offline repack, include/b200_q4f16.h B200_LAYOUT_PAIRED).  Stated here from the definition,
+# nibble by nibble, to check the device permutation against.
+PAIRED_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)
+
+
+def repack_paired(wq: np.ndarray) -> np.ndarray:
+    """Reference nibble order -> paired layout, same shape."""
+    q = unpack_nibbles(wq).reshape(wq.shape[0], -1, 8)
+    return pack_nibbles(q[:, :, list(PAIRED_ORDER)].reshape(wq.shape[0], -1))
+
+
+def unpack_paired(packed: np.ndarray) -> np.ndarray:
+    """Paired layout -> reference nibble order."""
+    q = unpack_nibbles(packed).reshape(packed.shape[0], -1, 8)
+    inv = np.argsort(np.array(PAIRED_ORDER))
+    return pack_nibbles(q[:, :, inv].reshape(packed.shape[0], -1))
+
+
 def dequantize(wq: np.ndarray, scales: np.ndarray, group: int = 32) -> np.ndarray:
     """fp16 [N,K] = (q - 7) * scale, one fp16 rounding."""
     q = unpack_nibbles(wq).astype(np.int32) - 7

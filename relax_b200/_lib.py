@@ -14,6 +14,12 @@ LIB_PATH = os.environ.get("B200_Q4F16_LIB") or os.path.join(_HERE, "libb200_q4f1
 OK, EINVAL, ENODEVICE, ELAUNCH, EDEVICE, ENOTREADY = 0, -1, -2, -3, -4, -5
 ATTN_EARLY_KV_LOADS = 1   # B200_ATTN_EARLY_KV_LOADS
 FAMILY_AUTO, FAMILY_GEMV, FAMILY_GEMM = 0, 1, 2
+LAYOUT_REFERENCE, LAYOUT_PAIRED = 0, 1
+
+
+def family_with_layout(family, layout):
+    """The `family` argument of b200_q4f16_matmul_dl_family that also names the weight layout of the call."""
+    return family | ((layout + 1) << 8)
 
 
 class B200Error(RuntimeError):
@@ -94,6 +100,10 @@ PROTOTYPES = {
     "b200_q4f16_matmul_dl": (_ci, [_dlp, _dlp, _dlp, _dlp]),
     "b200_q4f16_dequantize_dl": (_ci, [_dlp, _dlp, _dlp]),
     "b200_q4f16_matmul_dl_family": (_ci, [_dlp, _dlp, _dlp, _dlp, ctypes.c_int32]),
+    "b200_q4f16_repack": (_ci, [_vp, _vp, _i64, _i64, ctypes.c_int32, _vp]),
+    "b200_q4f16_unpack": (_ci, [_vp, _vp, _i64, _i64, ctypes.c_int32, _vp]),
+    "b200_q4f16_matmul_layout": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int32, _vp]),
+    "b200_q4f16_dequantize_layout": (_ci, [_vp, _vp, _vp, _i64, _i64, ctypes.c_int32, _vp]),
     "b200_q4f16_matmul_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_dequantize_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_gemv_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),

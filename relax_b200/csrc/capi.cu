@@ -29,6 +29,13 @@ Options& options() {
   return o;
 }
 
+thread_local int g_call_layout = -1;
+int current_layout() { return g_call_layout >= 0 ? g_call_layout : (int)options().weights_layout; }
+LayoutScope::LayoutScope(int layout) : saved(g_call_layout) {
+  if (layout >= 0) g_call_layout = layout;
+}
+LayoutScope::~LayoutScope() { g_call_layout = saved; }
+
 // Per-process cache of "device d is usable" (index = device ordinal).
 int ensure_device() {
   static int ok[64] = {0};
@@ -109,9 +116,12 @@ int matmul_impl(Family fam, const char* who, const void* x, const void* wq, cons
   if (M == 0 || N == 0) return B200_OK;
   if (K == 0) return zero_output(y, M, N, s);
   bool use_gemv = fam == kGemv || (fam == kAuto && M <= 16);
-  // 9..16 batch rows with a long K: the skinny kernel would have to restage x in several K blocks
-  // (16 rows x K no longer fit beside its ring); the weight-stationary kernel streams x instead
-  if (fam == kAuto && M >= 9 && M <= 16 && M * K * 2 > 160 * 1024 && K % 256 == 0 && options().gemm_ws_max_m >= M) {
+  // 9..16 batch rows: the skinny kernel stages all of x in every CTA (and restages it in K blocks once 16 rows x K
+  // no longer fit beside its ring); the weight-stationary kernel streams x through a ring instead.  Measured on
+  // B200 it is the faster one wherever its K split is in use (N up to about 8192: 9.8 against 12.1 us at
+  // N = K = 4096, 16.4 against 29.5 at K = 11008) and always when x does not fit; with many row tiles the skinny
+  // kernel wins (24.8 against 39 us at N = 22016).
+  if (fam == kAuto && M >= 9 && M <= 16 && (N <= 8192 || M * K * 2 > 160 * 1024) && K % 256 == 0 && options().gemm_ws_max_m >= M) {
     rc = launch_gemm_ws(static_cast<const __half*>(x), static_cast<const uint32_t*>(wq), static_cast<const __half*>(scales),
                         static_cast<__half*>(y), M, N, K, s);
     if (rc != B200_ENOTREADY) return rc;
@@ -121,10 +131,9 @@ int matmul_impl(Family fam, const char* who, const void* x, const void* wq, cons
   auto sh = static_cast<const __half*>(scales);
   auto yh = static_cast<__half*>(y);
   if (use_gemv) return launch_gemv(xh, wh, sh, yh, M, N, K, s);
-  // Mid-sized batches with few weight rows: the prefill kernel would have only N/256 tiles to spread
-  // over the SMs, the weight-stationary kernel splits K over a cluster instead (measured faster up to
-  // N of about 8192 on B200; beyond that the prefill kernel's tiles fill the GPU).
-  if (fam == kGemmWs || (fam == kAuto && M <= options().gemm_ws_max_m && N <= 8192)) {
+  // Mid-sized batches (up to 128 rows): the weights stream once whatever the batch, which the prefill kernel's
+  // 256-token tiles would waste (measured at M = 64: 23.7 against 51 us at N = 12288, 46 against 51 at N = 22016).
+  if (fam == kGemmWs || (fam == kAuto && M <= options().gemm_ws_max_m)) {
     rc = launch_gemm_ws(xh, wh, sh, yh, M, N, K, s);
     if (rc != B200_ENOTREADY) return rc;
     if (fam == kGemmWs) return fail(B200_EINVAL, "%s: the weight-stationary kernel takes 1 <= M <= 128, K %% 256 == 0, 16-byte aligned scales", who);
@@ -231,7 +240,7 @@ int host_copy(const void* src, void* dst, size_t bytes, bool dependent, cudaStre
 extern "C" {
 
 const char* b200_last_error(void) { return g_err; }
-int b200_abi_version(void) { return 101; }
+int b200_abi_version(void) { return 102; }
 
 int b200_set_stream(void* s) {
   g_stream = static_cast<cudaStream_t>(s);
@@ -263,7 +272,12 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "layer.stages")) { if (v < 0 || v > 5) return fail(B200_EINVAL, "layer.stages in 0..5"); o.layer_stages = v; }
   else if (!strcmp(name, "layer.max_ctas")) { if (v < 0 || v > 1024) return fail(B200_EINVAL, "layer.max_ctas in 0..1024"); o.layer_max_ctas = v; }
   else if (!strcmp(name, "gemm.ws_ksplit")) { if (v < 0 || v > 8 || (v & (v - 1))) return fail(B200_EINVAL, "gemm.ws_ksplit is 0, 1, 2, 4 or 8"); o.gemm_ws_ksplit = v; }
+  else if (!strcmp(name, "gemm.ws_x_stages")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemm.ws_x_stages in 0..8"); o.gemm_ws_x_stages = v; }
+  else if (!strcmp(name, "gemm.ws_w_stages")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemm.ws_w_stages in 0..8"); o.gemm_ws_w_stages = v; }
+  else if (!strcmp(name, "gemm.ws_r_stages")) { if (v < 0 || v == 1 || v > 8) return fail(B200_EINVAL, "gemm.ws_r_stages is 0 or in 2..8"); o.gemm_ws_r_stages = v; }
+  else if (!strcmp(name, "gemm.ws_xk")) { if (v != 0 && v != 2 && v != 4) return fail(B200_EINVAL, "gemm.ws_xk is 0, 2 or 4"); o.gemm_ws_xk = v; }
   else if (!strcmp(name, "gemm.ws_max_m")) { if (v < 0 || v > 128) return fail(B200_EINVAL, "gemm.ws_max_m in 0..128"); o.gemm_ws_max_m = v; }
+  else if (!strcmp(name, "weights.layout")) { if (v != B200_LAYOUT_REFERENCE && v != B200_LAYOUT_PAIRED) return fail(B200_EINVAL, "weights.layout is 0 (reference) or 1 (paired)"); o.weights_layout = v; }
   else if (!strcmp(name, "gemm.max_ctas")) { if (v < 0 || v > 1024) return fail(B200_EINVAL, "gemm.max_ctas in 0..1024"); o.gemm_max_ctas = v; }
   else return fail(B200_EINVAL, "set_option: unknown option '%s'", name);
   return B200_OK;
@@ -285,6 +299,11 @@ int64_t b200_get_option(const char* name) {
   if (!strcmp(name, "layer.max_ctas")) return o.layer_max_ctas;
   if (!strcmp(name, "gemm.ws_ksplit")) return o.gemm_ws_ksplit;
   if (!strcmp(name, "gemm.ws_max_m")) return o.gemm_ws_max_m;
+  if (!strcmp(name, "gemm.ws_x_stages")) return o.gemm_ws_x_stages;
+  if (!strcmp(name, "gemm.ws_w_stages")) return o.gemm_ws_w_stages;
+  if (!strcmp(name, "gemm.ws_xk")) return o.gemm_ws_xk;
+  if (!strcmp(name, "gemm.ws_r_stages")) return o.gemm_ws_r_stages;
+  if (!strcmp(name, "weights.layout")) return o.weights_layout;
   return -1;
 }
 
@@ -297,6 +316,56 @@ int b200_q4f16_dequantize(const void* wq, const void* scales, void* w_out, int64
   if (rc) return rc;
   return launch_dequantize(static_cast<const uint32_t*>(wq), static_cast<const __half*>(scales),
                            static_cast<__half*>(w_out), N, K, static_cast<cudaStream_t>(stream));
+}
+
+static int check_layout(const char* who, int32_t layout) {
+  if (layout != B200_LAYOUT_REFERENCE && layout != B200_LAYOUT_PAIRED)
+    return fail(B200_EINVAL, "%s: unknown weight layout %d (0 reference, 1 paired)", who, (int)layout);
+  return B200_OK;
+}
+
+static int repack_impl(const char* who, const void* in, void* out, int64_t N, int64_t K, int32_t layout, bool to_layout,
+                       void* stream) {
+  int rc = check_layout(who, layout);
+  if (rc) return rc;
+  if (N < 0 || K < 0) return fail(B200_EINVAL, "%s: negative shape N=%lld K=%lld", who, (long long)N, (long long)K);
+  if (K % 32 != 0) return fail(B200_EINVAL, "%s: K=%lld is not a multiple of the group size 32", who, (long long)K);
+  if (N > 0 && K > 0 && (!in || !out)) return fail(B200_EINVAL, "%s: null pointer", who);
+  if (((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 3u) != 0)
+    return fail(B200_EINVAL, "%s: buffers must be 4-byte aligned", who);
+  if (N > 0 && K > 0 && in != out) {
+    const char* a = static_cast<const char*>(in);
+    const char* b = static_cast<const char*>(out);
+    const int64_t bytes = N * (K / 2);
+    if (a < b + bytes && b < a + bytes) return fail(B200_EINVAL, "%s: input and output overlap without being the same buffer", who);
+  }
+  if ((rc = ensure_device())) return rc;
+  return launch_repack(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), N * (K / 8), layout, to_layout,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int b200_q4f16_repack(const void* wq, void* packed_out, int64_t N, int64_t K, int32_t layout, void* stream) {
+  return repack_impl("q4f16_repack", wq, packed_out, N, K, layout, true, stream);
+}
+
+int b200_q4f16_unpack(const void* packed, void* wq_out, int64_t N, int64_t K, int32_t layout, void* stream) {
+  return repack_impl("q4f16_unpack", packed, wq_out, N, K, layout, false, stream);
+}
+
+int b200_q4f16_matmul_layout(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                             int32_t layout, void* stream) {
+  int rc = check_layout("q4f16_matmul_layout", layout);
+  if (rc) return rc;
+  LayoutScope scope(layout);
+  return matmul_impl(kAuto, "q4f16_matmul_layout", x, wq, scales, y, M, N, K, stream);
+}
+
+int b200_q4f16_dequantize_layout(const void* wq, const void* scales, void* w_out, int64_t N, int64_t K, int32_t layout,
+                                 void* stream) {
+  int rc = check_layout("q4f16_dequantize_layout", layout);
+  if (rc) return rc;
+  LayoutScope scope(layout);
+  return b200_q4f16_dequantize(wq, scales, w_out, N, K, stream);
 }
 
 int b200_q4f16_matmul(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
@@ -426,8 +495,14 @@ int b200_q4f16_matmul_dl_family(const B200DLTensor* x, const B200DLTensor* wq, c
                                 int32_t family) {
   const char* who = "b200.q4f16_matmul";
   int dev = -1, rc;
+  // bits 0-7: kernel family; bits 8-15: weight layout + 1 (0 = the process-wide option)
+  const int32_t layout_code = (family >> 8) & 0xff;
+  if ((family & ~0xffff) != 0 || layout_code > 2)
+    return fail(B200_EINVAL, "%s: malformed family/layout code 0x%x", who, (unsigned)family);
+  family &= 0xff;
   if (family != B200_FAMILY_AUTO && family != B200_FAMILY_GEMV && family != B200_FAMILY_GEMM)
     return fail(B200_EINVAL, "%s: unknown kernel family %d (0 auto, 1 skinny, 2 tensor-core)", who, (int)family);
+  LayoutScope scope(layout_code - 1);
   if ((rc = check_tensor(who, "x", x, 2, 16, &dev))) return rc;
   if ((rc = check_tensor(who, "wq", wq, 1, 32, &dev))) return rc;
   if ((rc = check_tensor(who, "scales", scales, 2, 16, &dev))) return rc;

@@ -106,6 +106,7 @@ struct LayerParams {
   const int* step;                       // device scalar that grows by one per decode step
   uint64_t wait_ns;
   int nstages, kmax;
+  int paired;                            // nibble order of the packed words (q4_common.cuh)
   LayerPeer peer_o, peer_down;
 };
 
@@ -655,13 +656,8 @@ q4f16_decode_layer_kernel(const __grid_constant__ LayerParams p) {
   };
   // one staged word (eight activations) in the order the unpack produces; returns its offset sum
   auto stage_word = [&](int j, const uint4& v) -> float {
-    uint4 q;
-    q.x = __byte_perm(v.x, v.z, 0x5410);
-    q.y = __byte_perm(v.x, v.z, 0x7632);
-    q.z = __byte_perm(v.y, v.w, 0x5410);
-    q.w = __byte_perm(v.y, v.w, 0x7632);
-    xs[XL::slot(j, 0)] = q;
-    return offset_sum_f16x8(v);
+    xs[XL::slot(j, 0)] = staged_order(v, p.paired != 0);
+    return offset_sum_f16x8(v, p.paired != 0);
   };
   auto store_group_sum = [&](int grp, float psum) {
     const int ci = corr_index(grp);
@@ -955,6 +951,7 @@ int b200_decode_layer(const B200DecodeLayer* a, void* stream) {
   p.qkv = (__half*)a->qkv; p.attn = (__half*)a->attn; p.o = (__half*)a->o; p.x_out = (__half*)a->x_out;
   p.act = (__half*)a->act; p.down = (__half*)a->down;
   p.norm1 = (const __half*)a->norm1; p.norm2 = (const __half*)a->norm2; p.eps = a->eps;
+  p.paired = current_layout() == kLayoutPaired;
   p.cos_t = (const float*)a->cos_t; p.sin_t = (const float*)a->sin_t; p.pos = (const int*)a->pos;
   p.k_cache = (__half*)a->k_cache; p.v_cache = (__half*)a->v_cache;
   p.nh = nh; p.max_ctx = (int)a->max_ctx;

@@ -165,6 +165,7 @@ __device__ __forceinline__ void wait_or_abort_relaxed(uint64_t* bar, uint32_t pa
   }
 }
 
+template <bool PAIRED>   // nibble order of the packed words (q4_common.cuh): the paired order needs no byte permutes
 __global__ void __launch_bounds__(kNumThreads, 1)
 q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ unsigned char smem_unaligned[];
@@ -391,7 +392,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const uint4 o = q4_dequant_natural(words[c], c < 4 ? s_lo : s_hi, qc);
+          const uint4 o = q4_dequant_ordered<PAIRED>(words[c], c < 4 ? s_lo : s_hi, qc);
           *reinterpret_cast<uint4*>(brow + ((c ^ r8) << 4)) = o;
         }
         fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's async proxy
@@ -447,7 +448,7 @@ int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __hal
   if (grid > 2 * tiles) grid = 2 * tiles;
   else if (grid > tiles && grid < 2 * tiles) grid = tiles;
   const size_t smem = sizeof(Smem) + 1024;
-  auto kern = q4f16_gemm_tcgen05_kernel;
+  auto kern = current_layout() == kLayoutPaired ? q4f16_gemm_tcgen05_kernel<true> : q4f16_gemm_tcgen05_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemm: cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
   kern<<<grid, kNumThreads, smem, stream>>>(p);

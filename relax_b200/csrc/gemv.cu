@@ -21,6 +21,7 @@
 // the fp32 summation order differs from the reference's sequential loop.
 #include "internal.h"
 #include "q4_common.cuh"
+#include "skinny_common.cuh"
 
 namespace b200 {
 
@@ -67,7 +68,7 @@ template <int NC, int RT>
 __global__ void __launch_bounds__(512)
 q4f16_gemv_stream_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ wq,
                          const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
-                         int kblk) {
+                         int kblk, int paired) {
   constexpr int MT = (NC + 7) / 8;           // n8 column tiles
   constexpr int TILE_N = 16 * RT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -150,12 +151,8 @@ q4f16_gemv_stream_kernel(const __half* __restrict__ x, const uint32_t* __restric
         int k = k0 + j * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (m < M && k < K) v = *reinterpret_cast<const uint4*>(x + (int64_t)m * K + k);
-        uint4 p;
-        p.x = __byte_perm(v.x, v.z, 0x5410);   // (k0,k4)
-        p.y = __byte_perm(v.x, v.z, 0x7632);   // (k1,k5)
-        p.z = __byte_perm(v.y, v.w, 0x5410);   // (k2,k6)
-        p.w = __byte_perm(v.y, v.w, 0x7632);   // (k3,k7)
-        xs[x_slot<NC>(j, m)] = p;
+        // (k0,k4)(k1,k5)(k2,k6)(k3,k7) for the reference's nibble order, natural order for the paired layout
+        xs[x_slot<NC>(j, m)] = skinny::staged_order(v, paired != 0);
       }
     }
     __syncthreads();
@@ -256,7 +253,7 @@ int launch_stream(const __half* x, const uint32_t* wq, const __half* scales, __h
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = options().gemv_pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, x, wq, scales, y, M, N, K, kblk);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, x, wq, scales, y, M, N, K, kblk, (int)(current_layout() == kLayoutPaired));
   if (e != cudaSuccess) return fail(B200_ELAUNCH, "gemv launch: %s", cudaGetErrorString(e));
   count_launch();
   return B200_OK;

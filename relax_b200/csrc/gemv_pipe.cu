@@ -92,6 +92,7 @@ struct PipeParams {
   const __half* norm_w;      // RmsNorm: weight [K]
   __half* x_out;             // RmsNorm: fp16(x + delta) is written here by CTA 0 (or null)
   float eps;
+  int paired;                // nibble order of the packed words: 0 reference, 1 paired (q4_common.cuh)
   PeerReduce red;
 };
 
@@ -448,13 +449,8 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   // Stores one staged word (eight activations of one batch column) in the permuted order the unpack
   // produces; the fast form also returns its offset sum.
   auto stage_word = [&](int j, int m, const uint4& v) -> float {
-    uint4 q;
-    q.x = __byte_perm(v.x, v.z, 0x5410);
-    q.y = __byte_perm(v.x, v.z, 0x7632);
-    q.z = __byte_perm(v.y, v.w, 0x5410);
-    q.w = __byte_perm(v.y, v.w, 0x7632);
-    xs[XL::slot(j, m)] = q;
-    return FAST ? offset_sum_f16x8(v) : 0.f;
+    xs[XL::slot(j, m)] = staged_order(v, p.paired != 0);
+    return FAST ? offset_sum_f16x8(v, p.paired != 0) : 0.f;
   };
   // Fast form (one batch column): minus the offset sum of scale group `grp`, twice (rows g and g+8 of the
   // accumulator fragment).
@@ -847,6 +843,7 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   p.M = M; p.N = N; p.K = K;
   p.delta = pro.delta; p.norm_w = pro.norm_w; p.x_out = pro.x_out; p.eps = pro.eps;
   p.red = red;
+  p.paired = current_layout() == kLayoutPaired;
   p.ntiles = (N + kRows - 1) / kRows;
   const int kpad = ((K + KC - 1) / KC) * KC;
   const int stages_per_tile = kpad / KC;

@@ -26,13 +26,29 @@ struct Options {
   int64_t layer_max_ctas = 0;   // layer kernel: cap on the grid (0 = one CTA per SM); tests use small grids
   int64_t gemm_max_ctas = 0;  // 0 = one per SM; smaller values force several tiles per CTA (tests)
   int64_t gemm_ws_ksplit = 0; // 0 = auto: K slices (= cluster size) of the weight-stationary kernel
+  int64_t weights_layout = 0; // B200_LAYOUT_*: the nibble order every matmul entry point assumes unless the call names one
+  int64_t gemm_ws_x_stages = 0; // 0 = auto: cap on the depth of the weight-stationary kernel's x ring
+  int64_t gemm_ws_w_stages = 0; // 0 = auto (2): depth of its dequantised-weight ring
+  int64_t gemm_ws_r_stages = 0; // 0 = auto: cap on the depth of its packed-weight ring (>= 2)
+  int64_t gemm_ws_xk = 0;       // 0 = auto: K blocks per stage of its x and dequantised rings (2 or 4)
   int64_t gemm_ws_max_m = 128; // largest M the automatic dispatch gives to the weight-stationary kernel (0 = never)
 };
 Options& options();
 
+// Weight layout of the matmul being launched on this thread: the call's own (entry points that carry a layout
+// set it for their duration through LayoutScope), else the process-wide option.
+int current_layout();
+struct LayoutScope {
+  explicit LayoutScope(int layout);   // layout < 0: keep the option's
+  ~LayoutScope();
+  int saved;
+};
+
 // Kernel launchers: arguments validated by the caller, pointers are device pointers.
 int launch_dequantize(const uint32_t* wq, const __half* scales, __half* w, int64_t N, int64_t K,
                       cudaStream_t stream);
+// Word-wise permutation between the reference's nibble order and `layout` (to_layout = true: reference -> layout).
+int launch_repack(const uint32_t* in, uint32_t* out, int64_t n_words, int layout, bool to_layout, cudaStream_t stream);
 int launch_gemv(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
 // Skinny matmul with a neighbour of the decoder layer fused into the staging of x (1 <= M <= 16,

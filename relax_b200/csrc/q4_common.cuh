@@ -78,4 +78,33 @@ __device__ __forceinline__ uint4 q4_dequant_natural(uint32_t w, __half2 scale2, 
   return o;
 }
 
+// Weight layouts.  kLayoutReference: nibble j of a word is k % 8 = j (what the reference's encoder writes,
+// python/tvm/relax/transform/legalize_ops.py in its tree does the decode the same way).  kLayoutPaired: the
+// nibbles of a word sit in the order k0,k2,k4,k6,k1,k3,k5,k7, so that the four mask-and-or extractions of
+// q4_unpack_pairs yield (k0,k1) (k2,k3) (k4,k5) (k6,k7): natural order without the four byte permutes.
+// Same shape, same scales; a pure permutation inside every 32-bit word (b200_q4f16_repack / _unpack).
+constexpr int kLayoutReference = 0, kLayoutPaired = 1;
+
+// Reference word -> paired word and back (each is the other's inverse).
+__host__ __device__ __forceinline__ uint32_t q4_word_to_paired(uint32_t w) {
+  // nibble positions [0..7] of the result hold k0,k2,k4,k6,k1,k3,k5,k7
+  return (w & 0xFu) | ((w >> 4) & 0xF0u) | ((w >> 8) & 0xF00u) | ((w >> 12) & 0xF000u) |
+         ((w << 12) & 0xF0000u) | ((w << 8) & 0xF00000u) | ((w << 4) & 0xF000000u) | (w & 0xF0000000u);
+}
+__host__ __device__ __forceinline__ uint32_t q4_word_from_paired(uint32_t v) {
+  return (v & 0xFu) | ((v >> 12) & 0xF0u) | ((v << 4) & 0xF00u) | ((v >> 8) & 0xF000u) |
+         ((v << 8) & 0xF0000u) | ((v >> 4) & 0xF00000u) | ((v << 12) & 0xF000000u) | (v & 0xF0000000u);
+}
+
+// Dequantised word of the PAIRED layout in natural order: the four pairs are already (k0,k1) .. (k6,k7).
+__device__ __forceinline__ uint4 q4_dequant_paired(uint32_t w, __half2 scale2, const Q4Consts& c) {
+  uint32_t p[4];
+  q4_dequant_pairs(w, scale2, p, c);
+  return make_uint4(p[0], p[1], p[2], p[3]);
+}
+template <bool PAIRED>
+__device__ __forceinline__ uint4 q4_dequant_ordered(uint32_t w, __half2 scale2, const Q4Consts& c) {
+  return PAIRED ? q4_dequant_paired(w, scale2, c) : q4_dequant_natural(w, scale2, c);
+}
+
 }  // namespace b200

@@ -101,11 +101,24 @@ struct XLayout {
 // Offsets the raw nibble halves carry in the fast form: (w & 0x000F000F) | 0x64006400 = 1024 + q (even k of a
 // word), (w & 0x00F000F0) | 0x54005400 = 64 + q (odd k); minus the zero point 7 that is 1031 and 71.
 constexpr float kOffEven = 1031.f, kOffOdd = 71.f;
-// sum over the eight k of one staged word of x_k * offset_k; v holds (x0,x1)(x2,x3)(x4,x5)(x6,x7)
-__device__ __forceinline__ float offset_sum_f16x8(const uint4& v) {
+// sum over the eight k of one staged word of x_k * offset_k; v holds (x0,x1)(x2,x3)(x4,x5)(x6,x7).  In the paired
+// weight layout the 1024-offset extractions hold k0,k1,k4,k5 and the 64-offset ones k2,k3,k6,k7.
+__device__ __forceinline__ float offset_sum_f16x8(const uint4& v, bool paired) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
   const float2 a = __half22float2(h[0]), b = __half22float2(h[1]), c = __half22float2(h[2]), d = __half22float2(h[3]);
+  if (paired) return fmaf(kOffEven, (a.x + a.y) + (c.x + c.y), kOffOdd * ((b.x + b.y) + (d.x + d.y)));
   return fmaf(kOffEven, (a.x + c.x) + (b.x + d.x), kOffOdd * ((a.y + c.y) + (b.y + d.y)));
+}
+// One word of activations (x0..x7) in the order the unpack of a packed weight word produces its four pairs:
+// (k0,k4)(k1,k5)(k2,k6)(k3,k7) for the reference's nibble order, natural order for the paired layout.
+__device__ __forceinline__ uint4 staged_order(const uint4& v, bool paired) {
+  if (paired) return v;
+  uint4 q;
+  q.x = __byte_perm(v.x, v.z, 0x5410);
+  q.y = __byte_perm(v.x, v.z, 0x7632);
+  q.z = __byte_perm(v.y, v.w, 0x5410);
+  q.w = __byte_perm(v.y, v.w, 0x7632);
+  return q;
 }
 // Where the fast form keeps minus the offset sum of group `grp` (counted from the start of the staged block):
 // 32 floats per 256-k chunk, [lane pair t & 1][set: even / odd group][c0 c1 c0 c1], so that lane (g,t) fetches

@@ -26,7 +26,7 @@ def test_header_symbols_all_exported_and_bound():
     for s in syms:
         assert hasattr(handle, s), f"{s} declared in include/b200_q4f16.h but not exported"
     assert sorted(_lib.PROTOTYPES) == syms, "ctypes prototypes out of sync with the header"
-    assert _lib.lib().b200_abi_version() == 101
+    assert _lib.lib().b200_abi_version() == 102
 
 
 def _cpu_case(m=2, n=16, k=64):
@@ -138,3 +138,37 @@ def test_options_roundtrip():
     relax_b200.set_option("gemv.warps", 0)
     with pytest.raises(relax_b200.B200Error):
         relax_b200.set_option("no.such.option", 1)
+
+
+def test_weight_file_format_cpu(tmp_path):
+    """The on-disk container of packed weights: round trip, alignment of the payload, and the errors of a
+    damaged file (host logic only)."""
+    import numpy as np
+
+    from relax_b200 import synth, weights_io
+
+    _, wq, s = synth.make_case(1, 24, 320, seed=3)
+    p = str(tmp_path / "w.b2q4")
+    weights_io.save(p, {"m": (wq, s), "empty": (np.zeros((0, 4), np.uint32), np.zeros((0, 1), np.float16))}, "paired")
+    layout, t = weights_io.load(p)
+    assert layout == "paired" and (t["m"][0] == wq).all() and (t["m"][1].view(np.uint16) == s.view(np.uint16)).all()
+    assert t["empty"][0].shape == (0, 4)
+    raw = open(p, "rb").read()
+    hlen = int.from_bytes(raw[12:16], "little")
+    assert (16 + hlen) % 64 == 0
+    import pytest
+
+    with pytest.raises(ValueError):
+        weights_io.save(p, {"m": (wq, s[:, :5])})
+    with pytest.raises(ValueError):
+        weights_io.save(p, {"m": (wq, s)}, "swizzled")
+    bad = str(tmp_path / "bad.b2q4")
+    open(bad, "wb").write(b"NOTAFILE" + raw[8:])
+    with pytest.raises(weights_io.FormatError):
+        weights_io.load(bad)
+    open(bad, "wb").write(raw[:8] + (9).to_bytes(4, "little") + raw[12:])
+    with pytest.raises(weights_io.FormatError):
+        weights_io.load(bad)
+    open(bad, "wb").write(raw[:-100])
+    with pytest.raises(weights_io.FormatError):
+        weights_io.load(bad)
