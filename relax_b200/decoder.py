@@ -101,7 +101,7 @@ class DecodeEngine:
     """
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
-                 device, rank: int = 0, world: int = 1, group=None, fused: bool = True, peer_reduce: bool = True,
+                 device, rank: int = 0, world: int = 1, group=None, fused=None, peer_reduce: bool = True,
                  fused_attention=False, guard=None, verify: bool = True, layer_kernel=None):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
@@ -120,8 +120,11 @@ class DecodeEngine:
         hl = H // world
         il_max = max(l["inter_local"] for l in layers) if layers else cfg.inter
         # fused: RMSNorm (+ residual add) and SwiGLU run inside the staging of the next skinny matmul
-        # (7 kernels per layer instead of 11); needs batch <= 16, the skinny kernel's range
-        self.fused = bool(fused) and B <= 16
+        # (7 kernels per layer instead of 11); needs batch <= 16, the skinny kernel's range.  By default only at
+        # batch 1: every CTA of a fused kernel recomputes the statistics of all the batch's rows, and from two rows on
+        # the separate kernels are faster (measured per layer at context 2000: 80 against 88 us at batch 2, 124 against
+        # 176 at batch 8, 174 against 291 at batch 16).
+        self.fused = (B == 1) if fused is None else (bool(fused) and B <= 16)
         # False: rotary/append, attention, merge as three launches; True: one launch; "rope": rotary/append
         # inside the attention launch, merge as a second launch
         self.fused_attention = "rope" if fused_attention == "rope" else bool(fused_attention)
