@@ -30,6 +30,8 @@ relax_b200/tvm_plugin/src/relax/backend/contrib/b200/codegen.cc.
 
 Options (the map given to ``RunCodegen({"b200": {...}})``, run_codegen.cc:42,155):
     "family": "auto" (default) | "gemv" | "gemm"    kernel family the wrapper asks for
+    "weight_layout": "reference" | "paired"          nibble order of the bound weights (the offline repack of
+                                                     b200_q4f16_repack); absent = the library's option "weights.layout"
 """
 from __future__ import annotations
 
@@ -47,6 +49,8 @@ class B200CodegenError(ValueError):
 
 
 FAMILIES = {"auto": 0, "gemv": 1, "gemm": 2}
+# code added to the family argument of b200_q4f16_matmul_dl_family (bits 8-15 = layout + 1, B200_FAMILY_WITH_LAYOUT)
+WEIGHT_LAYOUTS = {"reference": (0 + 1) << 8, "paired": (1 + 1) << 8}
 
 # decode PrimFuncs whose body has been compared with the canonical decode: name -> layout.
 # Filled by partition_for_b200 / validate_decodes; the codegen refuses call_tir to any other name.
@@ -202,10 +206,16 @@ def analyze_function(func, options=None) -> Q4Plan:
     family = str(options.pop("family", "auto"))
     if family not in FAMILIES:
         raise B200CodegenError(f"b200: option family={family!r}; expected one of {sorted(FAMILIES)}")
+    layout_code = 0
+    if "weight_layout" in options:
+        layout = str(options.pop("weight_layout"))
+        if layout not in WEIGHT_LAYOUTS:
+            raise B200CodegenError(f"b200: option weight_layout={layout!r}; expected one of {sorted(WEIGHT_LAYOUTS)}")
+        layout_code = WEIGHT_LAYOUTS[layout]
     if options:
-        raise B200CodegenError(f"b200: unknown codegen option(s) {sorted(options)}; known: ['family']")
+        raise B200CodegenError(f"b200: unknown codegen option(s) {sorted(options)}; known: ['family', 'weight_layout']")
     symbol = str(func.attrs["global_symbol"])
-    plan = Q4Plan(symbol, len(func.params), [], FAMILIES[family])
+    plan = Q4Plan(symbol, len(func.params), [], FAMILIES[family] | layout_code)
     source = {p: ("param", i) for i, p in enumerate(func.params)}
     local = {}
     last_var = None

@@ -94,7 +94,7 @@ def q4f16_matmul_patterns(decodes):
 
 def partition_for_b200(mod, options=None, merge=False):
     """Offloads every q4f16 decode->matmul->astype group to relax.ext.b200.  options: {"family":
-    "auto"|"gemv"|"gemm"}.  merge=True runs MergeCompositeFunctions so that chained matmuls share one
+    "auto"|"gemv"|"gemm", "weight_layout": "reference"|"paired"}.  merge=True runs MergeCompositeFunctions so that chained matmuls share one
     offloaded function."""
     found = decode_layouts(mod)
     if not found:

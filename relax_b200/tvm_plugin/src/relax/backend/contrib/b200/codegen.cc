@@ -22,6 +22,8 @@
  * canonical one before its name enters the pattern table and passes the verdict in the option map:
  *     options["decode_layouts"] = {"<primfunc name>": "nk" | "kn"}   ([N,K] needs permute_dims, [K,N] must not have it)
  *     options["family"]         = "auto" | "gemv" | "gemm"            (kernel family the wrapper asks for)
+ *     options["weight_layout"]  = "reference" | "paired"              (nibble order of the bound weights after the
+ *                                                                      offline repack; absent = the library's option)
  * A call_tir to a name that is not in the map is refused.
  *
  * The returned module is a CSourceModule ("cc") per function whose code unpacks the DLTensor
@@ -212,6 +214,19 @@ int FamilyOf(const Map<String, ObjectRef>& options) {
   return 0;
 }
 
+// Bits 8-15 of the family argument: weight layout + 1 (B200_FAMILY_WITH_LAYOUT in b200_q4f16.h), 0 = the library's option.
+int LayoutBitsOf(const Map<String, ObjectRef>& options) {
+  auto it = options.find("weight_layout");
+  if (it == options.end()) return 0;
+  const auto* s = (*it).second.as<StringObj>();
+  ICHECK(s) << "relax.ext.b200: option \"weight_layout\" must be a string";
+  std::string v(s->data, s->size);
+  if (v == "reference") return (0 + 1) << 8;
+  if (v == "paired") return (1 + 1) << 8;
+  LOG(FATAL) << "relax.ext.b200: option weight_layout=\"" << v << "\"; expected reference or paired";
+  return 0;
+}
+
 }  // namespace
 
 Array<runtime::Module> B200Compiler(Array<Function> functions, Map<String, ObjectRef> options,
@@ -219,8 +234,9 @@ Array<runtime::Module> B200Compiler(Array<Function> functions, Map<String, Objec
   const auto* create = runtime::Registry::Get("runtime.CSourceModuleCreate");
   ICHECK(create) << "runtime.CSourceModuleCreate is not registered";
   for (const auto& kv : options)
-    ICHECK(kv.first == "family" || kv.first == "decode_layouts") << "relax.ext.b200: unknown option " << kv.first;
-  const int family = FamilyOf(options);
+    ICHECK(kv.first == "family" || kv.first == "decode_layouts" || kv.first == "weight_layout")
+        << "relax.ext.b200: unknown option " << kv.first;
+  const int family = FamilyOf(options) | LayoutBitsOf(options);
   Map<String, ObjectRef> decode_layouts;
   if (options.count("decode_layouts")) decode_layouts = Downcast<Map<String, ObjectRef>>(options["decode_layouts"]);
 

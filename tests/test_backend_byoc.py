@@ -177,6 +177,14 @@ def test_codegen_options():
         backend.partition_for_b200(q4_module(2, 64, 128), options={"family": "warp-speed"})
     with pytest.raises(Exception, match="unknown codegen option"):
         backend.partition_for_b200(q4_module(2, 64, 128), options={"tile": "128"})
+    # the layout of weights repacked offline travels in bits 8-15 of the family argument (layout + 1)
+    backend.partition_for_b200(q4_module(2, 64, 128), options={"family": "gemv", "weight_layout": "paired"})
+    assert backend.codegen.COMPILED[SYMBOL].family == (1 | (2 << 8))
+    assert ", 513) != 0" in backend.emit_wrapper(backend.codegen.COMPILED[SYMBOL])
+    backend.partition_for_b200(q4_module(2, 64, 128), options={"weight_layout": "reference"})
+    assert backend.codegen.COMPILED[SYMBOL].family == (1 << 8)
+    with pytest.raises(Exception, match="weight_layout"):
+        backend.partition_for_b200(q4_module(2, 64, 128), options={"weight_layout": "zigzag"})
 
 
 def test_unvalidated_decode_name_is_refused_by_the_codegen():
@@ -278,6 +286,25 @@ def test_relax_vm_runs_the_offloaded_module_on_the_gpu(M, N, K, options):
     y = vm["main"](*_on_gpu(x, wq, s))
     torch.cuda.synchronize()
     assert_matmul_close(y.numpy(), x, wq, s, f"relax vm M={M}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 40])
+def test_relax_vm_on_weights_repacked_offline(M):
+    """Weights bound in the paired layout (b200_q4f16_repack): the codegen option names the layout, the VM's
+    result is the one of the reference's words."""
+    import torch
+
+    from relax_b200 import ops, synth
+    from util import assert_matmul_close
+
+    N, K = 512, 1024
+    vm = _gpu_vm(backend.partition_for_b200(q4_module(M, N, K), options={"weight_layout": "paired"}))
+    x, wq, s = synth.make_case(M, N, K, seed=6)
+    packed = ops.q4f16_repack(torch.from_numpy(wq).cuda(), "paired").cpu().numpy()
+    y = vm["main"](*_on_gpu(x, packed, s))
+    torch.cuda.synchronize()
+    assert_matmul_close(y.numpy(), x, wq, s, f"relax vm, paired weights, M={M}")
 
 
 @pytest.mark.gpu
