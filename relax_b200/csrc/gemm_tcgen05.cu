@@ -232,56 +232,98 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
+      // The whole warp walks the loop (waits, cursors, descriptor arithmetic are warp-uniform, so the compiler can
+      // keep them on the uniform datapath); only the tcgen05 instructions themselves are issued by one lane.
+      const bool leader = lane == 0;
       constexpr uint32_t idesc = umma_idesc_f16_f32(BM, BN);
-      uint32_t it_a = 0, it_b = 0, it_tile = 0;
+      // The issue of a tcgen05.mma holds this thread until the tensor core takes the instruction, so the time of
+      // this loop's own instructions ADDS to the MMAs' time (measured with a micro-benchmark, and a lone thread
+      // spends 10-15 clocks per instruction, more on a taken branch).  Hence: straight-line code per K block, one
+      // branch for both waits, ring cursors advanced by selects, descriptors by 32-bit adds to the address field
+      // (bits 0-13, in 16-byte units; every operand sits below 256 KB, so nothing carries out of the field), the
+      // first K block of a tile (which waits for the drained accumulators) peeled out of the loop.
+      const uint64_t dconst = umma_desc_k128(0);
+      const uint32_t a_base = (smem_u32(sm.a[0]) & 0x3FFFFu) >> 4, b_base = (smem_u32(sm.b[0]) & 0x3FFFFu) >> 4;
+      constexpr uint32_t a_step = kABytes >> 4, b_step = kBBytes >> 4, half_off = (BM * BK * 2) >> 4;
+      uint32_t sa = 0, pa = 0, sb = 0, pb = 0;              // stage and phase of the x ring and of the dequantised ring
+      uint32_t it_tile = 0;
+      auto operands_ready = [&]() {
+        const bool ready = mbar_try_wait(&sm.a_full[sa], pa) & mbar_try_wait(&sm.b_full[sb], pb);
+        if (!ready) {
+          wait_or_abort(&sm.a_full[sa], pa, abort_flag, 5);
+          wait_or_abort(&sm.b_full[sb], pb, abort_flag, 6);
+        }
+        tc_fence_after_sync();
+      };
+      auto release_and_advance = [&]() {
+        if (leader) umma_commit(&sm.a_empty[sa]);
+        if (leader) umma_commit(&sm.b_empty[sb]);
+        sa = sa + 1 == SA ? 0 : sa + 1;
+        pa ^= (uint32_t)(sa == 0);
+        sb = sb + 1 == SB ? 0 : sb + 1;
+        pb ^= (uint32_t)(sb == 0);
+      };
       Work w;
       for (int i = 0; get_work(p, i, w); ++i, ++it_tile) {
         const int nhalf = w.nhalf;                            // second half all padding or not ours: skip it
-        for (int kb = 0; kb < num_kb; ++kb, ++it_a, ++it_b) {
-          const int sa = it_a % SA, sb = it_b % SB;
-          wait_or_abort(&sm.a_full[sa], (it_a / SA) & 1, abort_flag, 5);
-          wait_or_abort(&sm.b_full[sb], (it_b / SB) & 1, abort_flag, 6);
-          tc_fence_after_sync();
-          const uint64_t db = umma_desc_k128(smem_u32(sm.b[sb]));
-          if (kb > 0 && nhalf == 2) {
-            // Both halves' accumulators are ours from the first K block on: issue the two
-            // independent accumulation chains alternately (measured 2-5 % faster than one
-            // half after the other).
-            const uint64_t da0 = umma_desc_k128(smem_u32(sm.a[sa]));
-            const uint64_t da1 = umma_desc_k128(smem_u32(sm.a[sa] + BM * BK * 2));
+        // ---- first K block: each half's accumulator must have been drained by the epilogue of the tile before
+        {
+          operands_ready();
+          const uint64_t db = dconst | (uint64_t)(b_base + sb * b_step);
+          for (int h = 0; h < nhalf; ++h) {
+            if (it_tile > 0) {
+              wait_or_abort(&sm.acc_empty[h], (it_tile - 1) & 1, abort_flag, 4);
+              tc_fence_after_sync();
+            }
+            const uint64_t da = dconst | (uint64_t)(a_base + sa * a_step + h * half_off);
 #pragma unroll
             for (int k16 = 0; k16 < BK / 16; ++k16) {
-              umma_f16_ss(tmem_base, da0 + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, 1);
-              umma_f16_ss(tmem_base + (uint32_t)BN, da1 + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, 1);
-            }
-            if (kb == num_kb - 1) {
-              umma_commit(&sm.acc_full[0]);
-              umma_commit(&sm.acc_full[1]);
-            }
-          } else {
-            for (int h = 0; h < nhalf; ++h) {
-              if (kb == 0 && it_tile > 0) {
-                // the epilogue has drained this half of the previous tile
-                wait_or_abort(&sm.acc_empty[h], (it_tile - 1) & 1, abort_flag, 4);
-                tc_fence_after_sync();
-              }
-              const uint32_t d_tmem = tmem_base + (uint32_t)h * BN;
-              const uint64_t da = umma_desc_k128(smem_u32(sm.a[sa] + h * (BM * BK * 2)));
-#pragma unroll
-              for (int k16 = 0; k16 < BK / 16; ++k16) {
-                // advancing 16 fp16 along K inside the swizzled 128-byte row = +32 bytes = +2 in the
-                // descriptor's 16-byte address units
-                umma_f16_ss(d_tmem, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, (kb | k16) != 0);
-              }
-              if (kb == num_kb - 1) umma_commit(&sm.acc_full[h]);
+              // advancing 16 fp16 along K inside the swizzled 128-byte row = +32 bytes = +2 in the
+              // descriptor's 16-byte address units
+              if (leader) umma_f16_ss(tmem_base + (uint32_t)h * BN, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, k16 != 0);
             }
           }
-          umma_commit(&sm.a_empty[sa]);
-          umma_commit(&sm.b_empty[sb]);
+          if (num_kb == 1) {
+            if (leader) umma_commit(&sm.acc_full[0]);
+            if (nhalf == 2 && leader) umma_commit(&sm.acc_full[1]);
+          }
+          release_and_advance();
+        }
+        // ---- the other K blocks
+        if (nhalf == 2) {
+          // Both halves' accumulators are ours: the two independent accumulation chains are issued alternately
+          // (measured 2-5 % faster than one half after the other).
+          for (int kb = 1; kb < num_kb; ++kb) {
+            operands_ready();
+            const uint64_t da0 = dconst | (uint64_t)(a_base + sa * a_step);
+            const uint64_t da1 = da0 + (uint64_t)half_off;
+            const uint64_t db = dconst | (uint64_t)(b_base + sb * b_step);
+#pragma unroll
+            for (int k16 = 0; k16 < BK / 16; ++k16) {
+              if (leader) umma_f16_ss(tmem_base, da0 + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, 1);
+              if (leader) umma_f16_ss(tmem_base + (uint32_t)BN, da1 + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, 1);
+            }
+            if (kb == num_kb - 1) {
+              if (leader) umma_commit(&sm.acc_full[0]);
+              if (leader) umma_commit(&sm.acc_full[1]);
+            }
+            release_and_advance();
+          }
+        } else {
+          for (int kb = 1; kb < num_kb; ++kb) {
+            operands_ready();
+            const uint64_t da = dconst | (uint64_t)(a_base + sa * a_step);
+            const uint64_t db = dconst | (uint64_t)(b_base + sb * b_step);
+#pragma unroll
+            for (int k16 = 0; k16 < BK / 16; ++k16)
+              if (leader) umma_f16_ss(tmem_base, da + (uint64_t)(2 * k16), db + (uint64_t)(2 * k16), idesc, 1);
+            if (kb == num_kb - 1 && leader) umma_commit(&sm.acc_full[0]);
+            release_and_advance();
+          }
         }
         // a skipped half still takes part in the hand-shake so that the parities stay in step
-        if (nhalf == 1) umma_commit(&sm.acc_full[1]);
+        if (nhalf == 1 && leader) umma_commit(&sm.acc_full[1]);
       }
     }
   } else if ((warp >= 4 && warp < 8) || warp >= 24) {
