@@ -377,7 +377,9 @@ def run_decode(args, world, rank, dev, batches):
             "kernels_per_step": eng.kernels_per_step(), "engine": "one persistent kernel per layer" if eng.layer_kernel else
             "fused prologues, skinny kernels" if eng.fused else
             "separate RMSNorm/SwiGLU kernels, mid-batch tensor-core matmul",
-            "lm_head": "fp16, tied to the embedding, vocabulary-sharded (library GEMM)",
+            "lm_head": ("fp16, tied to the embedding, vocabulary-sharded; this library's kernel (b200_lm_head)"
+                        + (", greedy token inside it" if world == 1 else ", torch argmax over the gathered slices")
+                        if batch <= 16 else "fp16, tied to the embedding, vocabulary-sharded (library GEMM + torch argmax above 16 rows)"),
             "allreduce": (None if world == 1 else "fused into the o/down matmul kernels over NVLink peer memory (fp16 partials, "
                           "rank-order sum)" if eng.peer is not None else "NCCL fp16, 2 per layer"), "steps": steps,
             "parity_max_rel": parity,

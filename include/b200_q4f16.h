@@ -143,6 +143,19 @@ B200_API int b200_q4f16_dequantize_dl(const B200DLTensor* wq, const B200DLTensor
 B200_API int b200_q4f16_matmul_dl_family(const B200DLTensor* x, const B200DLTensor* wq, const B200DLTensor* scales,
                                          B200DLTensor* y, int32_t family);
 
+/* ---- output projection of a decode step -------------------------------------------------
+ * logits fp16 [B, V] = h fp16 [B, H] . w fp16 [V, H]^T, fp32 accumulation, one RN-even rounding: the reference's
+ * generic matmul + astype (python/tvm/relax/transform/legalize_ops.py:203-264, 157-162) on an unquantised
+ * table, for 1 <= B <= 16 rows (above that a library GEMM is the right tool).  H % 32 == 0, 16-byte aligned
+ * pointers.  `logits` may be NULL when only the tokens are wanted.  With `tokens` != NULL the kernel also
+ * writes the greedy choice of every row, token_offset + argmax over the V rows of THIS table (ties: the lowest
+ * index), which needs `scratch`: b200_lm_head_scratch_bytes() bytes of device memory, zeroed once by the caller
+ * and left zeroed-where-it-matters by every call; calls that share a scratch buffer must be ordered (one stream).
+ * Allocates nothing. */
+B200_API int64_t b200_lm_head_scratch_bytes(void);
+B200_API int b200_lm_head(const void* h, const void* w, void* logits, int32_t* tokens, void* scratch, int64_t B,
+                          int64_t V, int64_t H, int64_t token_offset, void* stream);
+
 /* ---- offline weight repack --------------------------------------------------------------
  * The reference binds weights into the executable as constants when it builds
  * (python/tvm/relax/vm.py:620-629 hands `const_name_to_constant` to the external codegen's modules), so a

@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200_q4f16.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-SOURCES = ["capi.cu", "tmap.cu", "dequant.cu", "gemv.cu", "gemv_pipe.cu", "gemm_tcgen05.cu", "gemm_ws_tcgen05.cu", "decoder_ops.cu", "decode_layer.cu"]
+SOURCES = ["capi.cu", "tmap.cu", "dequant.cu", "gemv.cu", "gemv_pipe.cu", "gemm_tcgen05.cu", "gemm_ws_tcgen05.cu", "decoder_ops.cu", "decode_layer.cu", "lm_head.cu"]
 HEADERS = ["internal.h", "q4_common.cuh", "sm100_ptx.cuh", "tmap.h", "skinny_common.cuh"]
 
 NVCC_FLAGS = [

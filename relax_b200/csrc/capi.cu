@@ -344,6 +344,30 @@ static int repack_impl(const char* who, const void* in, void* out, int64_t N, in
                        static_cast<cudaStream_t>(stream));
 }
 
+int64_t b200_lm_head_scratch_bytes(void) {
+  if (ensure_device()) return -1;
+  return lm_head_scratch_bytes();
+}
+
+int b200_lm_head(const void* h, const void* w, void* logits, int32_t* tokens, void* scratch, int64_t B, int64_t V,
+                 int64_t H, int64_t token_offset, void* stream) {
+  if (B < 1 || B > 16) return fail(B200_EINVAL, "lm_head: takes 1 <= B <= 16 rows, got %lld", (long long)B);
+  if (V < 1 || V > 0x7fffff00LL || H < 32 || H % 32 != 0)
+    return fail(B200_EINVAL, "lm_head: need 1 <= V < 2^31, H >= 32 and H %% 32 == 0 (V=%lld H=%lld)", (long long)V, (long long)H);
+  if (!h || !w || (!logits && !tokens)) return fail(B200_EINVAL, "lm_head: null pointer (h, w, and one of logits / tokens are required)");
+  if (tokens && !scratch) return fail(B200_EINVAL, "lm_head: tokens need the scratch buffer (b200_lm_head_scratch_bytes)");
+  if (!aligned16(h) || !aligned16(w) || (scratch && !aligned16(scratch)) || (reinterpret_cast<uintptr_t>(logits) & 1u) ||
+      (reinterpret_cast<uintptr_t>(tokens) & 3u))
+    return fail(B200_EINVAL, "lm_head: h, w and scratch must be 16-byte aligned");
+  if (token_offset < 0 || token_offset + V > 0x7fffffffLL) return fail(B200_EINVAL, "lm_head: token_offset + V overflows int32");
+  int rc = ensure_device();
+  if (rc) return rc;
+  rc = launch_lm_head(static_cast<const __half*>(h), static_cast<const __half*>(w), static_cast<__half*>(logits), tokens,
+                      static_cast<float*>(scratch), B, V, H, token_offset, static_cast<cudaStream_t>(stream));
+  if (rc == B200_ENOTREADY) return fail(B200_EINVAL, "lm_head: %lld rows of H=%lld do not fit in shared memory", (long long)B, (long long)H);
+  return rc;
+}
+
 int b200_q4f16_repack(const void* wq, void* packed_out, int64_t N, int64_t K, int32_t layout, void* stream) {
   return repack_impl("q4f16_repack", wq, packed_out, N, K, layout, true, stream);
 }

@@ -65,6 +65,12 @@ int launch_gemm_ws(const __half* x, const uint32_t* wq, const __half* scales, __
 int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                 int64_t K, cudaStream_t stream);
 
+// fp16 output projection of a decode step (1 <= B <= 16) with optional greedy sampling; B200_ENOTREADY when the
+// activations do not fit in shared memory.
+int launch_lm_head(const __half* x, const __half* w, __half* logits, int* tokens, float* scratch, int64_t B, int64_t V,
+                   int64_t H, int64_t token_offset, cudaStream_t stream);
+int64_t lm_head_scratch_bytes();
+
 // Reads and clears the per-kernel device error words (bit 0-7: skinny pipeline, 8-15: tensor-core GEMM, 16-23: weight-stationary GEMM,
 // 24-30: decoder-layer kernel).
 int device_error_flags_read_and_clear();

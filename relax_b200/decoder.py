@@ -2,8 +2,9 @@
 matmul (RMSNorm, RoPE + KV cache, attention, SwiGLU) wired to the C-ABI kernels, optionally
 tensor-parallel with one NCCL all-reduce after each row-parallel matmul.
 
-torch is used for device memory, streams, CUDA graphs, the NCCL process group and the fp16
-lm_head GEMM (a plain library GEMM); every other kernel of a step is this library's.
+torch is used for device memory, streams, CUDA graphs and the NCCL process group; every kernel of a step is
+this library's for batches of up to 16 (above that the fp16 output projection is a plain library GEMM, and under
+tensor parallelism the sampling over the gathered vocabulary slices is torch's argmax).
 
 Layout per rank (world size t, hidden H, heads nh, head dim 128, intermediate I):
 
@@ -149,6 +150,7 @@ class DecodeEngine:
         self.logits_local = torch.zeros((B, vl), **f16) if vl else None
         self.logits = torch.zeros((B, vl * world), **f16) if vl and world > 1 else self.logits_local
         self.gathered = torch.zeros((world, B, vl), **f16) if vl and world > 1 else None
+        self.lm_scratch = torch.zeros((max(int(self.L.b200_lm_head_scratch_bytes()), 16) // 4,), dtype=torch.float32, device=self.device)
         self.graph = None
         self.launches_per_step = 0
         # batch 1: one persistent kernel per layer (b200_decode_layer) instead of seven launches.  Off by default:
@@ -335,20 +337,29 @@ class DecodeEngine:
         self._check(L.b200_rmsnorm(xlast.data_ptr(), delta.data_ptr() if delta is not None else None,
                                    self.final_norm.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.eps, sp))
         if self.lm_head is not None:
-            torch.matmul(self.h, self.lm_head.t(), out=self.logits_local)
+            own = B <= 16                       # the library's output projection takes up to 16 rows; above that a library GEMM
+            if own:
+                toks = self.tokens.data_ptr() if self.world == 1 else None
+                self._check(L.b200_lm_head(self.h.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), toks,
+                                           self.lm_scratch.data_ptr(), B, self.lm_head.shape[0], cfg.hidden, 0, sp))
+            else:
+                torch.matmul(self.h, self.lm_head.t(), out=self.logits_local)
             if self.world > 1:
                 # gather the vocabulary slices: [world, B, V_l] -> [B, world * V_l]
                 torch.distributed.all_gather_into_tensor(self.gathered, self.logits_local, group=self.group)
                 self.logits.view(B, self.world, -1).copy_(self.gathered.permute(1, 0, 2))
-            self.tokens.copy_(torch.argmax(self.logits, dim=1).to(torch.int32))
+            if not own or self.world > 1:
+                self.tokens.copy_(torch.argmax(self.logits, dim=1).to(torch.int32))
         self._check(L.b200_advance_pos(self.pos.data_ptr(), 1, sp))
         self._check(L.b200_advance_pos(self.epoch.data_ptr(), 1, sp))
 
     def kernels_per_step(self) -> int:
-        """Kernels of this library launched by one step (embed + 5 or 11 per layer + final norm + advance)."""
+        """Kernels of this library launched by one step (embed + 5 or 11 per layer + final norm + output projection
+        for up to 16 rows + advance)."""
+        head = 1 if self.lm_head is not None and self.batch <= 16 else 0
         if self.layer_kernel:
-            return 1 + len(self.layers) + 1 + 2
-        return 1 + len(self.layers) * ((5 if self.fused else 9) + (1 if self.fused_attention == "rope" else (0 if self.fused_attention else 2))) + 1 + 2
+            return 1 + len(self.layers) + 1 + head + 2
+        return 1 + len(self.layers) * ((5 if self.fused else 9) + (1 if self.fused_attention == "rope" else (0 if self.fused_attention else 2))) + 1 + head + 2
 
     def capture(self, stream):
         """Captures one step into a CUDA graph on `stream` (after one eager warm-up step, which

@@ -281,3 +281,53 @@ def test_decoder_graph_replay_matches_eager(cuda_lib):
     for a, b in zip(runs[0][0], runs[1][0]):
         assert (a == b).all()
     assert (runs[0][1].view(np.uint16) == runs[1][1].view(np.uint16)).all(), "graph replay must reproduce the eager step bit for bit"
+
+
+@pytest.mark.parametrize("B,V,H", [(1, 32000, 4096), (3, 1000, 512), (8, 4099, 1024), (9, 2048, 4096), (16, 32000, 4096), (2, 17, 32)])
+def test_lm_head_matches_oracle(cuda_lib, B, V, H):
+    """Output projection over an fp16 table: fp32 accumulation of exact products, one rounding to fp16 (the
+    reference's matmul + astype), and the greedy token = first maximum of the fp16 logits."""
+    rng = np.random.default_rng(B * 7 + V + H)
+    h = (0.5 * rng.standard_normal((B, H))).astype(np.float16)
+    w = (0.05 * rng.standard_normal((V, H))).astype(np.float16)
+    if V > 40:
+        w[V - 1] = w[7]                      # an exact tie between two rows: the lower index must win
+    th, tw = torch.from_numpy(h).cuda(), torch.from_numpy(w).cuda()
+    nbytes = cuda_lib.b200_lm_head_scratch_bytes()
+    assert nbytes > 0
+    scr = torch.zeros(nbytes // 4, dtype=torch.float32, device="cuda")
+    canary = 64
+    buf = torch.full((B * V + canary,), float("nan"), dtype=torch.float16, device="cuda")
+    toks = torch.full((B + 2,), -5, dtype=torch.int32, device="cuda")
+    for rep in range(2):                     # twice: the scratch counter must come back to zero by itself
+        assert cuda_lib.b200_lm_head(th.data_ptr(), tw.data_ptr(), buf.data_ptr(), toks.data_ptr(), scr.data_ptr(), B, V, H,
+                                     1000, 0) == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        logits = buf[:B * V].view(B, V).cpu().numpy()
+        assert torch.isnan(buf[B * V:]).all() and (toks[B:] == -5).all()
+        ref32 = h.astype(np.float32) @ w.astype(np.float32).T
+        absdot = np.abs(h.astype(np.float32)) @ np.abs(w.astype(np.float32)).T
+        err = np.abs(logits.astype(np.float64) - ref32.astype(np.float64))
+        assert (err <= 2.0 ** -10 * np.abs(ref32) + 8e-6 * absdot + 2.0 ** -24).all(), err.max()
+        want = np.argmax(logits.astype(np.float32), axis=1) + 1000      # numpy: first occurrence of the maximum
+        assert (toks[:B].cpu().numpy() == want).all(), (toks[:B].cpu().numpy(), want)
+    # logits only, tokens only
+    buf.fill_(float("nan"))
+    assert cuda_lib.b200_lm_head(th.data_ptr(), tw.data_ptr(), buf.data_ptr(), None, None, B, V, H, 0, 0) == 0
+    toks.fill_(-5)
+    assert cuda_lib.b200_lm_head(th.data_ptr(), tw.data_ptr(), None, toks.data_ptr(), scr.data_ptr(), B, V, H, 0, 0) == 0
+    torch.cuda.synchronize()
+    assert (buf[:B * V].view(B, V).cpu().numpy().view(np.uint16) == logits.view(np.uint16)).all()
+    assert (toks[:B].cpu().numpy() == want - 1000).all()
+
+
+def test_lm_head_argument_checks(cuda_lib):
+    t = torch.zeros(64 * 32, dtype=torch.float16, device="cuda")
+    p = t.data_ptr()
+    L = cuda_lib
+    assert L.b200_lm_head(p, p, p, None, None, 17, 4, 32, 0, 0) == _lib.EINVAL and "16 rows" in _lib.last_error()
+    assert L.b200_lm_head(p, p, p, None, None, 1, 4, 48, 0, 0) == _lib.EINVAL
+    assert L.b200_lm_head(p, p, None, None, None, 1, 4, 32, 0, 0) == _lib.EINVAL
+    assert L.b200_lm_head(p, p, None, p, None, 1, 4, 32, 0, 0) == _lib.EINVAL and "scratch" in _lib.last_error()
+    assert L.b200_lm_head(p + 2, p, p, None, None, 1, 4, 32, 0, 0) == _lib.EINVAL
+    assert L.b200_lm_head(p, p, p, None, None, 16, 4, 65536, 0, 0) == _lib.EINVAL and "shared memory" in _lib.last_error()
