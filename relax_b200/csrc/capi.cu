@@ -266,7 +266,7 @@ int b200_set_option(const char* name, int64_t v) {
   else if (!strcmp(name, "gemv.stages")) { if (v < 0 || v > 16) return fail(B200_EINVAL, "gemv.stages in 0..16"); o.gemv_stages = v; }
   else if (!strcmp(name, "gemv.pdl")) { o.gemv_pdl = v != 0; }
   else if (!strcmp(name, "gemv.ctas_per_sm")) { if (v < 0 || v > 8) return fail(B200_EINVAL, "gemv.ctas_per_sm in 0..8"); o.gemv_ctas_per_sm = v; }
-  else if (!strcmp(name, "gemv.exact")) { o.gemv_exact = v != 0; }
+  else if (!strcmp(name, "gemv.exact")) { if (v < 0 || v > 2) return fail(B200_EINVAL, "gemv.exact is 0 (by shape), 1 (exact form) or 2 (fast form)"); o.gemv_exact = v; }
   else if (!strcmp(name, "gemv.peer_wait_ms")) { if (v < 1 || v > 60000) return fail(B200_EINVAL, "gemv.peer_wait_ms in 1..60000"); o.gemv_peer_wait_ms = v; }
   else if (!strcmp(name, "layer.wait_ms")) { if (v < 1 || v > 60000) return fail(B200_EINVAL, "layer.wait_ms in 1..60000"); o.layer_wait_ms = v; }
   else if (!strcmp(name, "layer.stages")) { if (v < 0 || v > 5) return fail(B200_EINVAL, "layer.stages in 0..5"); o.layer_stages = v; }

@@ -960,8 +960,16 @@ template <int CW, int CH, int PRO>
 int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int m, int n, int k,
                   cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   if (m == 1) {
-    // batch 1: the fast form unless the caller asks for the reference's rounding of every weight
-    if (!options().gemv_exact) return launch_pipe<1, CW, CH, PRO, true>(x, wq, scales, y, m, n, k, stream, pro, red);
+    // batch 1: the fast form unless the caller asks for the reference's rounding of every weight (gemv.exact = 1)
+    // or, by default (gemv.exact = 0), K fills its last 4096-k stage poorly.  The fast form holds its first stage in
+    // registers BEFORE it stages x, so the arrival of the weights and the staging of x follow one another, which a
+    // short kernel does not win back: measured at N = 4096, exact / fast = 2.86 / 3.70 us at K = 512, 3.28 / 3.90 at
+    // 1536, 5.45 / 6.08 at 4608, 5.87 / 6.24 at 5632, against 4.55 / 4.35 at 3584, 4.88 / 4.49 at 4096, 7.07 / 6.67 at
+    // 8192, 8.94 / 8.73 at 11008.  gemv.exact = 2 forces the fast form for every K (tests).
+    const int stages = (k + CH * 256 - 1) / (CH * 256);
+    const bool fills = (int64_t)k * 100 >= (int64_t)stages * CH * 256 * 85;
+    const bool fast = options().gemv_exact == 2 || (options().gemv_exact == 0 && fills);
+    if (fast) return launch_pipe<1, CW, CH, PRO, true>(x, wq, scales, y, m, n, k, stream, pro, red);
     return launch_pipe<1, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);
   }
   if (m == 2) return launch_pipe<2, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);

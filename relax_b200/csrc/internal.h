@@ -19,7 +19,8 @@ struct Options {
   int64_t gemv_stages = 0;    // 0 = auto (bulk-copy pipeline depth)
   int64_t gemv_pdl = 1;       // programmatic dependent launch on the streaming kernels
   int64_t gemv_ctas_per_sm = 0;  // 0 = auto: cap on resident CTAs per SM used to size the grid
-  int64_t gemv_exact = 0;     // 1 = round every weight to fp16 as the reference does (the slower exact form of the skinny kernel)
+  int64_t gemv_exact = 0;     // batch-1 form of the skinny kernel: 0 = fast form where K fills its stages, exact form otherwise;
+                              // 1 = always round every weight to fp16 as the reference does (exact form); 2 = always the fast form
   int64_t gemv_peer_wait_ms = 2000;  // how long the fused sum over ranks waits for the other GPUs' flags
   int64_t layer_wait_ms = 2000; // layer kernel: how long a CTA waits at a stage counter, a peer flag or a weight stage
   int64_t layer_stages = 0;     // layer kernel: depth of the weight ring (0 = as many as fit, at most 5)

@@ -41,7 +41,7 @@ def skinny_form_is_unrounded(m) -> bool:
     kernel's fast form."""
     from relax_b200 import _lib
 
-    return m <= 16 and _lib.get_option("gemv.exact") == 0
+    return m <= 16 and _lib.get_option("gemv.exact") != 1
 
 
 def unrounded_slack(x, w):
