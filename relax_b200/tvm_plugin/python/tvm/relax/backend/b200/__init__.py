@@ -8,7 +8,7 @@ pattern helpers of python/tvm/relax/dpl/pattern.py:804-860,1049-1095).
 Patterns can only name a decode PrimFunc, and FuseOpsByPattern has no check callback in this tree, so
 what the PrimFunc computes is established here, before its name enters the table: it must be
 structurally equal to the canonical TE decode (zero point 7, low nibble first, one fp16 scale per 32
-elements of K).  The verdict travels to the C++ codegen in the option map ("decode_layouts").
+elements of K).  The result travels to the C++ codegen in the option map ("decode_layouts").
 """
 import tvm
 from tvm import relax, te, tir

@@ -19,7 +19,7 @@
  *
  * What the decode PrimFunc computes cannot be seen from here (the codegen receives functions, not the
  * module).  The Python half (python/tvm/relax/backend/b200) compares each decode PrimFunc with the
- * canonical one before its name enters the pattern table and passes the verdict in the option map:
+ * canonical one before its name enters the pattern table and passes the result in the option map:
  *     options["decode_layouts"] = {"<primfunc name>": "nk" | "kn"}   ([N,K] needs permute_dims, [K,N] must not have it)
  *     options["family"]         = "auto" | "gemv" | "gemm"            (kernel family the wrapper asks for)
  *     options["weight_layout"]  = "reference" | "paired"              (nibble order of the bound weights after the
