@@ -380,8 +380,11 @@ def run_decode(args, world, rank, dev, batches):
             "lm_head": ("fp16, tied to the embedding, vocabulary-sharded; this library's kernel (b200_lm_head)"
                         + (", greedy token inside it" if world == 1 else ", torch argmax over the gathered slices")
                         if batch <= 16 else "fp16, tied to the embedding, vocabulary-sharded (library GEMM + torch argmax above 16 rows)"),
-            "allreduce": (None if world == 1 else "fused into the o/down matmul kernels over NVLink peer memory (fp16 partials, "
-                          "rank-order sum)" if eng.peer is not None else "NCCL fp16, 2 per layer"), "steps": steps,
+            "allreduce": (None if world == 1 else "NCCL fp16, 2 per layer" if eng.peer is None else
+                          "fused into the o/down matmul kernels over NVLink peer memory (fp16 partials, rank-order sum)"
+                          if batch <= eng.PEER_FUSED_MAX_ROWS else
+                          "this library's peer-memory sum (b200_allreduce_peer) behind the o/down matmuls (fp16 partials, rank-order sum)"),
+            "steps": steps,
             "parity_max_rel": parity,
             "parity_against": None if args.no_decode_parity else
             f"one-GPU engine on rank 0 (unfused kernels, same seeds), logits of the first {bp} sequence(s) at position {parity_pos}: "

@@ -236,6 +236,13 @@ typedef struct {
 B200_API int b200_q4f16_gemv_allreduce(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
                                        int64_t K, int32_t swiglu, const B200PeerReduce* red, void* cuda_stream);
 
+/* The same sum as a kernel of its own, for partial results that another kernel of this library wrote (the
+ * mid-batch and prefill matmuls have no fused tail): out = sum over ranks of peer_y[r][0..count), fp16, in rank
+ * order.  The partial result peer_y[rank] must have been written by work that precedes this call in `stream`.
+ * Same descriptor and the same rules for flag slots and buffer reuse as above (`done_counter` is not used);
+ * count % 8 == 0; a wait that runs out sets the same error bit.  Every rank must make the matching call. */
+B200_API int b200_allreduce_peer(int64_t count, const B200PeerReduce* red, void* cuda_stream);
+
 /* ---- one decoder layer of a batch-1 decode step as ONE persistent kernel -----------------------------
  * The reference reaches a comparable effect when FuseOps folds a matmul's elementwise neighbours into its
  * group (src/relay/analysis/graph_partitioner.cc:285-296); it has no kernel that spans several matmuls.

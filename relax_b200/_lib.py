@@ -100,6 +100,7 @@ PROTOTYPES = {
     "b200_q4f16_matmul_dl": (_ci, [_dlp, _dlp, _dlp, _dlp]),
     "b200_q4f16_dequantize_dl": (_ci, [_dlp, _dlp, _dlp]),
     "b200_q4f16_matmul_dl_family": (_ci, [_dlp, _dlp, _dlp, _dlp, ctypes.c_int32]),
+    "b200_allreduce_peer": (_ci, [_i64, ctypes.POINTER(PeerReduce), _vp]),
     "b200_lm_head_scratch_bytes": (_i64, []),
     "b200_lm_head": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "b200_q4f16_repack": (_ci, [_vp, _vp, _i64, _i64, ctypes.c_int32, _vp]),

@@ -471,6 +471,22 @@ int b200_q4f16_gemv_allreduce(const void* x, const void* wq, const void* scales,
   return rc;
 }
 
+int b200_allreduce_peer(int64_t count, const B200PeerReduce* red, void* stream) {
+  const char* who = "allreduce_peer";
+  if (count < 0 || count % 8 != 0) return fail(B200_EINVAL, "%s: count must be a non-negative multiple of 8, got %lld", who, (long long)count);
+  if (!red) return fail(B200_EINVAL, "%s: null reduction descriptor", who);
+  if (red->world < 2 || red->world > 8 || red->rank < 0 || red->rank >= red->world)
+    return fail(B200_EINVAL, "%s: world %d / rank %d out of range (2..8)", who, red->world, red->rank);
+  if (!red->epoch || !red->out || !aligned16(red->out) || red->flag_base < 0)
+    return fail(B200_EINVAL, "%s: epoch and a 16-byte aligned out are required", who);
+  for (int r = 0; r < red->world; ++r)
+    if (!red->peer_y[r] || !aligned16(red->peer_y[r]) || !red->peer_flags[r])
+      return fail(B200_EINVAL, "%s: peer %d has a null or misaligned buffer", who, r);
+  int rc = ensure_device();
+  if (rc) return rc;
+  return launch_peer_allreduce(count, red, static_cast<cudaStream_t>(stream));
+}
+
 int b200_q4f16_gemm_ws(const void* x, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
                        void* stream) {
   return matmul_impl(kGemmWs, "q4f16_gemm_ws", x, wq, scales, y, M, N, K, stream);

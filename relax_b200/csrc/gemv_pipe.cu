@@ -993,6 +993,62 @@ int dispatch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __h
   return dispatch_form<kPrologueNone>(x, wq, scales, y, m, n, k, stream, pro, red);
 }
 
+// The sum over tensor-parallel ranks as a kernel of its own, for partial results that another kernel produced
+// (the mid-batch and prefill matmuls): same protocol as the tail of the skinny kernel above.  The partial result
+// peer_y[rank] was written by the launch in front of this one (stream order; with programmatic dependent launch
+// the wait below is what orders it).  CTA 0 publishes this rank's flag to every rank, every CTA waits (bounded)
+// for all ranks' flags and adds up its share of the `count` values in rank order with plain peer loads.
+__global__ void __launch_bounds__(256)
+peer_allreduce_kernel(int64_t n8, const PeerReduce red) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const int e = *red.epoch + 1;
+  if (tid < 32) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      if (tid < red.world) st_release_sys(red.peer_flags[tid] + red.flag_base + red.rank, e);
+    }
+    if (tid < red.world) {
+      const int* f = red.peer_flags[red.rank] + red.flag_base + tid;
+      const uint64_t t0 = globaltimer_ns();
+      while (ld_acquire_sys(f) < e) {
+        if (globaltimer_ns() - t0 > red.wait_ns) {     // a rank never published: give up, flag the error
+          atomicExch(&g_gemv_pipe_error, 16);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + tid; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 v[kMaxPeers];
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < red.world) v[r] = ld_volatile_v4(red.peer_y[r] + i * 8);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r) {
+      if (r < red.world) {
+        const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+    }
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(red.out + i * 8) = o;
+  }
+}
+
 PeerReduce make_reduce(const B200PeerReduce* r) {
   PeerReduce red;
   if (!r || r->world <= 1) return red;
@@ -1011,6 +1067,30 @@ PeerReduce make_reduce(const B200PeerReduce* r) {
 }
 
 }  // namespace
+
+int launch_peer_allreduce(int64_t count, const B200PeerReduce* r, cudaStream_t stream) {
+  const PeerReduce red = make_reduce(r);
+  const int64_t n8 = count >> 3;
+  if (n8 == 0) return B200_OK;
+  // never more CTAs than can be resident at once (they wait for the other ranks): a quarter of that is plenty for
+  // the few hundred KB this moves
+  int64_t grid = (n8 + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 2;
+  if (grid > cap) grid = cap;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = options().gemv_pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, n8, red);
+  if (e != cudaSuccess) return fail(B200_ELAUNCH, "peer all-reduce launch: %s", cudaGetErrorString(e));
+  count_launch();
+  return B200_OK;
+}
 
 // Returns B200_ENOTREADY when the shape is outside what this kernel takes (caller falls back to
 // the register-streaming kernel).

@@ -61,6 +61,9 @@ int launch_gemv_pipe_swiglu(const __half* gu, const uint32_t* wq, const __half* 
                             int64_t K, cudaStream_t stream);
 int launch_gemv_pipe_allreduce(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                                int64_t K, int swiglu, const B200PeerReduce* red, cudaStream_t stream);
+// Sum over tensor-parallel ranks of `count` fp16 values whose per-rank partial results sit in peer-mapped buffers
+// (protocol of B200PeerReduce).
+int launch_peer_allreduce(int64_t count, const B200PeerReduce* red, cudaStream_t stream);
 int launch_gemm_ws(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                    int64_t K, cudaStream_t stream);
 int launch_gemm(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,

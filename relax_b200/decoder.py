@@ -160,12 +160,12 @@ class DecodeEngine:
         self.layer_kernel = False if layer_kernel is None else bool(layer_kernel)
         if self.layer_kernel and B != 1:
             raise ValueError("the one-kernel-per-layer path is the batch-1 path")
-        # tensor parallel: the sum over ranks after o and down runs inside those matmul kernels over
-        # NVLink peer memory (b200_q4f16_gemv_allreduce) when the batch is in the skinny kernel's range;
-        # otherwise (or with peer_reduce=False) it is an NCCL all-reduce
+        # tensor parallel: the sum over ranks after o and down runs over NVLink peer memory, inside those matmul
+        # kernels (b200_q4f16_gemv_allreduce) for up to 8 rows, as a kernel of this library behind the mid-batch
+        # matmul above that (b200_allreduce_peer); with peer_reduce=False it is an NCCL all-reduce
         self.peer = None
         self.epoch = torch.zeros((1,), dtype=torch.int32, device=self.device)
-        if world > 1 and (peer_reduce or self.layer_kernel) and B <= 16:
+        if world > 1 and (peer_reduce or self.layer_kernel):
             self._setup_peer_reduce()
         if self.layer_kernel:
             self._setup_layer_kernel()
@@ -246,6 +246,16 @@ class DecodeEngine:
     def _matmul(self, x, w, y, n, k, sp):
         self._check(self.L.b200_q4f16_matmul(x.data_ptr(), w[0].data_ptr(), w[1].data_ptr(), y.data_ptr(), self.batch, n, k, sp))
 
+    # up to this many rows the sum over ranks runs inside the skinny matmul kernel; above, the matmul (mid-batch
+    # or prefill kernel) writes its partial result into the peer-mapped buffer and b200_allreduce_peer adds up
+    PEER_FUSED_MAX_ROWS = 8
+
+    def _matmul_then_peer_sum(self, kind: int, layer: int, x, w, out, n, k, sp):
+        d = self._reduce_desc(kind, layer, out)
+        self._check(self.L.b200_q4f16_matmul(x.data_ptr(), w[0].data_ptr(), w[1].data_ptr(), self.peer["y"][kind][self.rank],
+                                             self.batch, n, k, sp))
+        self._check(self.L.b200_allreduce_peer(self.batch * n, ctypes.byref(d), sp))
+
     def _allreduce(self, t):
         if self.world > 1:
             torch.distributed.all_reduce(t, group=self.group)
@@ -282,10 +292,12 @@ class DecodeEngine:
                                            self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx,
                                            _lib.ATTN_EARLY_KV_LOADS,   # rope_kv_append sits directly in front and waits first
                                            sp))
-        if self.peer is not None:
+        if self.peer is not None and B <= self.PEER_FUSED_MAX_ROWS:
             d = self._reduce_desc(0, i, self.o)
             self._check(L.b200_q4f16_gemv_allreduce(self.attn.data_ptr(), w["o"][0].data_ptr(), w["o"][1].data_ptr(),
                                                     self.peer["y"][0][self.rank], B, H, hl, 0, ctypes.byref(d), sp))
+        elif self.peer is not None:
+            self._matmul_then_peer_sum(0, i, self.attn, w["o"], self.o, H, hl, sp)
         else:
             self._matmul(self.attn, w["o"], self.o, H, hl, sp)
             self._allreduce(self.o)
@@ -305,10 +317,13 @@ class DecodeEngine:
                                        cfg.eps, sp))
             self._matmul(self.h, w["gu"], self.gu, 2 * il, H, sp)
             self._check(L.b200_silu_mul(self.gu.data_ptr(), self.act.data_ptr(), B, il, sp))
-            if self.peer is not None:
+            if self.peer is not None and B <= self.PEER_FUSED_MAX_ROWS:
                 d = self._reduce_desc(1, i, self.down)
                 self._check(L.b200_q4f16_gemv_allreduce(self.act.data_ptr(), w["down"][0].data_ptr(), w["down"][1].data_ptr(),
                                                         self.peer["y"][1][self.rank], B, H, il, 0, ctypes.byref(d), sp))
+                return self.down
+            if self.peer is not None:
+                self._matmul_then_peer_sum(1, i, self.act, w["down"], self.down, H, il, sp)
                 return self.down
             self._matmul(self.act, w["down"], self.down, H, il, sp)
         self._allreduce(self.down)

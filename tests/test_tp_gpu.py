@@ -51,19 +51,25 @@ def _worker(rank, world, port, ret, hidden, heads, inter):
         results = {}
         # "layer": batch 1 (the first sequence) through the one-kernel-per-layer path, whose sums over ranks run
         # inside the layer kernel
-        for name, w, peer in (("single", 1, False), ("nccl", world, False), ("peer", world, True), ("layer", world, True)):
+        # "peer-wide": 12 rows (the first two sequences repeated), above the range of the matmul kernel with the sum
+        # inside it: mid-batch matmul into the peer-mapped buffer + b200_allreduce_peer
+        wide = 12
+        for name, w, peer in (("single", 1, False), ("nccl", world, False), ("peer", world, True), ("layer", world, True),
+                              ("peer-wide", world, True)):
             r = 0 if w == 1 else rank
-            nb = 1 if name == "layer" else B
+            nb = 1 if name == "layer" else wide if name == "peer-wide" else B
             layers = [decoder.to_device(tp.shard_layer(l, r, w, cfg.hidden, cfg.inter), dev) for l in full]
             vl = cfg.vocab // w
             eng = decoder.DecodeEngine(cfg, layers, embed, fnorm, embed[r * vl:(r + 1) * vl].contiguous(), nb, max_ctx, dev,
                                        rank=r, world=w, peer_reduce=peer, layer_kernel=(name == "layer"))
             assert (eng.peer is not None) == peer and eng.layer_kernel == (name == "layer")
-            eng.tokens.copy_(torch.tensor(tokens[:nb], dtype=torch.int32))
+            assert (nb > eng.PEER_FUSED_MAX_ROWS) == (name == "peer-wide")
+            rows = [j % B for j in range(nb)]           # which of the oracle's sequences each row repeats
+            eng.tokens.copy_(torch.tensor([tokens[j] for j in rows], dtype=torch.int32))
             hs, ls = [], []
             for st in range(steps):
                 if st > 0:
-                    eng.tokens.copy_(torch.from_numpy(feed[st - 1][:nb]))
+                    eng.tokens.copy_(torch.from_numpy(feed[st - 1][rows]))
                 eng.step()
                 torch.cuda.synchronize()
                 hs.append(eng.h.float().cpu().numpy().copy())
@@ -73,15 +79,16 @@ def _worker(rank, world, port, ret, hidden, heads, inter):
             dist.barrier()
         if rank == 0:
             errs = {}
-            for name in ("single", "nccl", "peer", "layer"):
+            for name in ("single", "nccl", "peer", "layer", "peer-wide"):
                 e_or, e_l = 0.0, 0.0
                 nb = results[name][0][0].shape[0]
+                rows = [j % B for j in range(nb)]
                 for st in range(steps):
-                    h_ref = ref[st][0].astype(np.float32)[:nb]
-                    l_ref = ref[st][1].astype(np.float32)[:nb]
+                    h_ref = ref[st][0].astype(np.float32)[rows]
+                    l_ref = ref[st][1].astype(np.float32)[rows]
                     e_or = max(e_or, float(np.abs(results[name][0][st] - h_ref).max() / np.abs(h_ref).max()))
                     e_l = max(e_l, float(np.abs(results[name][1][st] - l_ref).max() / np.abs(l_ref).max()))
-                e_single = max(float(np.abs(a - b[:nb]).max() / np.abs(b[:nb]).max()) for a, b in zip(results[name][0], results["single"][0]))
+                e_single = max(float(np.abs(a - b[rows]).max() / np.abs(b[rows]).max()) for a, b in zip(results[name][0], results["single"][0]))
                 errs[name] = (e_or, e_l, e_single)
             ret["errs"] = errs
     finally:
