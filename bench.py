@@ -409,7 +409,7 @@ def run_decode(args, world, rank, dev, batches):
 NCU_TRAFFIC_BYTES = {
     ("gemv", 1, 4096, 4096): (9476352, "profiles/gemv_pipe_kernel__decode_gemv_M1_N4096_K4096.md (ncu capture, not re-measured by this run)"),
     ("gemv", 64, 4096, 4096): (10006272, "profiles/gemm_ws_tcgen05_kernel__mid_batch_M64_N4096_K4096.md (ncu capture, not re-measured by this run)"),
-    ("prefill", 2048, 11008, 4096): (42228224 + 2720768, "profiles/gemm_tcgen05_kernel__prefill_M2048_N11008_K4096.md (ncu capture, not re-measured by this run)"),
+    ("prefill", 2048, 11008, 4096): (42236416 + 2993664, "profiles/gemm_tcgen05_kernel__prefill_M2048_N11008_K4096.md (ncu capture, not re-measured by this run)"),
 }
 
 
