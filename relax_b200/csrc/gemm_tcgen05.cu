@@ -70,8 +70,11 @@ struct Smem {
   unsigned char a[SA][kABytes];
   unsigned char b[SB][kBBytes];
   unsigned char raw[SR][kRawBytes];
-  uint64_t a_full[SA], a_empty[SA];
-  uint64_t b_full[SB], b_empty[SB];
+  // The x ring and the dequantised ring advance one stage per K block in lock step (same depth), so stage s of
+  // both shares one pair of barriers: `full` collects the x load's bytes and the dequantiser warps' arrivals,
+  // `empty` is one tcgen05.commit that both the x producer and the dequantisers wait for.  One wait and one commit
+  // per K block for the MMA-issuing thread, whose own instructions add to the MMAs' time.
+  uint64_t full[SB], empty[SB];
   uint64_t raw_full[SR], raw_empty[SR];
   uint64_t acc_full[2], acc_empty[2];   // one pair per half
   uint32_t tmem_base;
@@ -179,8 +182,8 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
 
   if (tid == 0) {
     sm.abort_flag = 0;
-    for (int i = 0; i < SA; ++i) { mbar_init(&sm.a_full[i], 1); mbar_init(&sm.a_empty[i], 1); }
-    for (int i = 0; i < SB; ++i) { mbar_init(&sm.b_full[i], kDequantWarps); mbar_init(&sm.b_empty[i], 1); }
+    static_assert(SA == SB, "the x ring and the dequantised ring share their barriers");
+    for (int i = 0; i < SB; ++i) { mbar_init(&sm.full[i], 1 + kDequantWarps); mbar_init(&sm.empty[i], 1); }
     for (int i = 0; i < SR; ++i) { mbar_init(&sm.raw_full[i], 1); mbar_init(&sm.raw_empty[i], kDequantGroups * kDequantWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 8); }
     mbar_fence_init();
@@ -204,9 +207,9 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % SA;
           const uint32_t round = it / SA;
-          if (round > 0) wait_or_abort_relaxed(&sm.a_empty[s], (round - 1) & 1, abort_flag, 1);
-          mbar_arrive_expect_tx(&sm.a_full[s], kABytes);
-          tma_load_2d(sm.a[s], &p.tm_x, kb * BK, w.tok0, &sm.a_full[s]);
+          if (round > 0) wait_or_abort_relaxed(&sm.empty[s], (round - 1) & 1, abort_flag, 1);
+          mbar_arrive_expect_tx(&sm.full[s], kABytes);
+          tma_load_2d(sm.a[s], &p.tm_x, kb * BK, w.tok0, &sm.full[s]);
         }
       }
     }
@@ -240,27 +243,20 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       // The issue of a tcgen05.mma holds this thread until the tensor core takes the instruction, so the time of
       // this loop's own instructions ADDS to the MMAs' time (measured with a micro-benchmark, and a lone thread
       // spends 10-15 clocks per instruction, more on a taken branch).  Hence: straight-line code per K block, one
-      // branch for both waits, ring cursors advanced by selects, descriptors by 32-bit adds to the address field
+      // wait and one commit (the two rings share their barriers), ring cursors advanced by selects, descriptors by 32-bit adds to the address field
       // (bits 0-13, in 16-byte units; every operand sits below 256 KB, so nothing carries out of the field), the
       // first K block of a tile (which waits for the drained accumulators) peeled out of the loop.
       const uint64_t dconst = umma_desc_k128(0);
       const uint32_t a_base = (smem_u32(sm.a[0]) & 0x3FFFFu) >> 4, b_base = (smem_u32(sm.b[0]) & 0x3FFFFu) >> 4;
       constexpr uint32_t a_step = kABytes >> 4, b_step = kBBytes >> 4, half_off = (BM * BK * 2) >> 4;
-      uint32_t sa = 0, pa = 0, sb = 0, pb = 0;              // stage and phase of the x ring and of the dequantised ring
+      uint32_t sb = 0, pb = 0;                              // stage and phase of the two rings (they advance together)
       uint32_t it_tile = 0;
       auto operands_ready = [&]() {
-        const bool ready = mbar_try_wait(&sm.a_full[sa], pa) & mbar_try_wait(&sm.b_full[sb], pb);
-        if (!ready) {
-          wait_or_abort(&sm.a_full[sa], pa, abort_flag, 5);
-          wait_or_abort(&sm.b_full[sb], pb, abort_flag, 6);
-        }
+        wait_or_abort(&sm.full[sb], pb, abort_flag, 5);
         tc_fence_after_sync();
       };
       auto release_and_advance = [&]() {
-        if (leader) umma_commit(&sm.a_empty[sa]);
-        if (leader) umma_commit(&sm.b_empty[sb]);
-        sa = sa + 1 == SA ? 0 : sa + 1;
-        pa ^= (uint32_t)(sa == 0);
+        if (leader) umma_commit(&sm.empty[sb]);
         sb = sb + 1 == SB ? 0 : sb + 1;
         pb ^= (uint32_t)(sb == 0);
       };
@@ -276,7 +272,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
               wait_or_abort(&sm.acc_empty[h], (it_tile - 1) & 1, abort_flag, 4);
               tc_fence_after_sync();
             }
-            const uint64_t da = dconst | (uint64_t)(a_base + sa * a_step + h * half_off);
+            const uint64_t da = dconst | (uint64_t)(a_base + sb * a_step + h * half_off);
 #pragma unroll
             for (int k16 = 0; k16 < BK / 16; ++k16) {
               // advancing 16 fp16 along K inside the swizzled 128-byte row = +32 bytes = +2 in the
@@ -296,7 +292,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           // (measured 2-5 % faster than one half after the other).
           for (int kb = 1; kb < num_kb; ++kb) {
             operands_ready();
-            const uint64_t da0 = dconst | (uint64_t)(a_base + sa * a_step);
+            const uint64_t da0 = dconst | (uint64_t)(a_base + sb * a_step);
             const uint64_t da1 = da0 + (uint64_t)half_off;
             const uint64_t db = dconst | (uint64_t)(b_base + sb * b_step);
 #pragma unroll
@@ -313,7 +309,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         } else {
           for (int kb = 1; kb < num_kb; ++kb) {
             operands_ready();
-            const uint64_t da = dconst | (uint64_t)(a_base + sa * a_step);
+            const uint64_t da = dconst | (uint64_t)(a_base + sb * a_step);
             const uint64_t db = dconst | (uint64_t)(b_base + sb * b_step);
 #pragma unroll
             for (int k16 = 0; k16 < BK / 16; ++k16)
@@ -424,7 +420,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         // ---- this K block: words 8*(kb&1) .. +7 of pk, scale groups 2*(kb&3), 2*(kb&3)+1
         const int sb = it_b % SB;
         const uint32_t b_round = it_b / SB;
-        if (b_round > 0) wait_or_abort(&sm.b_empty[sb], (b_round - 1) & 1, abort_flag, 10);
+        if (b_round > 0) wait_or_abort(&sm.empty[sb], (b_round - 1) & 1, abort_flag, 10);
         const uint32_t scw = (kb & 2) ? ((kb & 1) ? sc4.w : sc4.z) : ((kb & 1) ? sc4.y : sc4.x);
         const __half2 scp = u32_as_h2(scw);
         const __half2 s_lo = __half2(__low2half(scp), __low2half(scp));
@@ -439,7 +435,7 @@ q4f16_gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         }
         fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.b_full[sb]);
+        if (lane == 0) mbar_arrive(&sm.full[sb]);
       }
     }
   }
