@@ -201,6 +201,17 @@ B200_API int32_t b200_q4f16_dequantize_packed(void* args, int* type_codes, int n
 B200_API int b200_q4f16_gemv_rmsnorm(const void* x, const void* delta, const void* norm_w, void* x_out, float eps,
                                      const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
                                      void* cuda_stream);
+/* gemv_rmsnorm for the qkv projection of ONE decode row, with b200_rope_kv_append in its epilogue: the matmul's
+ * rows are [q heads | k heads | v heads] (heads of 128); q is rotated (rotate-half pairing d <-> d+64, tables fp32
+ * [max_pos, 64], position *pos) into q_out fp16 [heads*128], the rotated key and the value of the new token go
+ * into k_cache / v_cache fp16 [max_ctx, heads, 128] at slot *pos; there is no qkv buffer.  Same arithmetic as the
+ * two separate kernels (the rotation works on the fp16-rounded matmul results).  Returns B200_ENOTREADY, with
+ * nothing launched, when this launch would not use the skinny kernel's fast form (option gemv.exact = 1, or a K
+ * that fills its stages poorly): call the two separate entry points then. */
+B200_API int b200_q4f16_gemv_rmsnorm_rope(const void* x, const void* delta, const void* norm_w, void* x_out, float eps,
+                                          const void* wq, const void* scales, const void* cos_t, const void* sin_t,
+                                          const void* pos, void* q_out, void* k_cache, void* v_cache, int64_t heads,
+                                          int64_t K, void* cuda_stream);
 B200_API int b200_q4f16_gemv_swiglu(const void* gu, const void* wq, const void* scales, void* y, int64_t M, int64_t N,
                                     int64_t K, void* cuda_stream);
 

@@ -110,6 +110,7 @@ PROTOTYPES = {
     "b200_q4f16_matmul_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_dequantize_packed": (ctypes.c_int32, [_vp, _ip, _ci, _vp, _ip, _vp]),
     "b200_q4f16_gemv_rmsnorm": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_q4f16_gemv_rmsnorm_rope": (_ci, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "b200_q4f16_gemv_swiglu": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_q4f16_gemv_allreduce": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int32, ctypes.POINTER(PeerReduce), _vp]),
     "b200_decode_layer_scratch_bytes": (_i64, [_i64, _i64]),

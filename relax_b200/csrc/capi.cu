@@ -426,6 +426,32 @@ int b200_q4f16_gemv_rmsnorm(const void* x, const void* delta, const void* norm_w
   return rc;
 }
 
+int b200_q4f16_gemv_rmsnorm_rope(const void* x, const void* delta, const void* norm_w, void* x_out, float eps, const void* wq,
+                                 const void* scales, const void* cos_t, const void* sin_t, const void* pos, void* q_out,
+                                 void* k_cache, void* v_cache, int64_t heads, int64_t K, void* stream) {
+  const char* who = "q4f16_gemv_rmsnorm_rope";
+  if (heads < 1 || heads > 4096) return fail(B200_EINVAL, "%s: heads %lld out of range", who, (long long)heads);
+  const int64_t N = 3 * heads * 128;
+  int rc = check_matmul(who, x, wq, scales, q_out, 1, N, K);
+  if (rc) return rc;
+  if (K < 256 || K % 256 != 0) return fail(B200_EINVAL, "%s: needs K a positive multiple of 256", who);
+  if (!aligned16(scales)) return fail(B200_EINVAL, "%s: scales must be 16-byte aligned", who);
+  if (!norm_w || !aligned16(norm_w)) return fail(B200_EINVAL, "%s: norm weight must be non-null and 16-byte aligned", who);
+  if ((delta && !aligned16(delta)) || (x_out && !aligned16(x_out))) return fail(B200_EINVAL, "%s: delta / x_out must be 16-byte aligned", who);
+  if (x_out == x) return fail(B200_EINVAL, "%s: x_out must not alias x (other CTAs still read x)", who);
+  if (!cos_t || !sin_t || !pos || !k_cache || !v_cache) return fail(B200_EINVAL, "%s: null table, position or cache pointer", who);
+  rc = ensure_device();
+  if (rc) return rc;
+  // B200_ENOTREADY (no message): the launch would not use the fast form; the caller runs b200_q4f16_gemv_rmsnorm and
+  // b200_rope_kv_append instead
+  return launch_gemv_pipe_rmsnorm_rope(static_cast<const __half*>(x), static_cast<const __half*>(delta),
+                                       static_cast<const __half*>(norm_w), static_cast<__half*>(x_out), eps,
+                                       static_cast<const uint32_t*>(wq), static_cast<const __half*>(scales),
+                                       static_cast<const float*>(cos_t), static_cast<const float*>(sin_t),
+                                       static_cast<const int*>(pos), static_cast<__half*>(q_out), static_cast<__half*>(k_cache),
+                                       static_cast<__half*>(v_cache), heads, K, static_cast<cudaStream_t>(stream));
+}
+
 int b200_q4f16_gemv_swiglu(const void* gu, const void* wq, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
                            void* stream) {
   const char* who = "q4f16_gemv_swiglu";

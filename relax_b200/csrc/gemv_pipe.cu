@@ -77,6 +77,20 @@ constexpr uint64_t kProducerWaitNs = 30000000000ull;    // 30 s: may span the pr
 
 enum { kPrologueNone = 0, kPrologueRmsNorm = 1, kPrologueSwiGLU = 2 };
 
+// Rotary embedding + KV append in the epilogue of the qkv matmul (batch 1, fast form).  The weight rows are then
+// fetched through a 5-D tensor map whose 16-row tile is dims d0..d0+7 of one 128-wide head AND their rotate-half
+// partners d0+64..d0+71, so a tile holds both members of every pair it produces (rows r and r + 8).
+struct RopeOut {
+  const float* cos_t = nullptr;   // fp32 [max_pos, 64]
+  const float* sin_t = nullptr;
+  const int* pos = nullptr;       // device scalar: position of the new token
+  __half* q_out = nullptr;        // [nh * 128] rotated query
+  __half* k_cache = nullptr;      // [max_ctx, nh, 128]: rotated key goes to slot *pos
+  __half* v_cache = nullptr;      // value likewise (not rotated)
+  int nh = 0;                     // heads of this rank: rows are q heads | k heads | v heads
+  int on = 0;
+};
+
 struct PipeParams {
   CUtensorMap tm_w;   // uint32 {32, N, K/256}, box {32, 16, CH}, 128B swizzle
   CUtensorMap tm_s;   // fp16   {8, N, K/256},  box {8, 16, CH}
@@ -93,6 +107,7 @@ struct PipeParams {
   __half* x_out;             // RmsNorm: fp16(x + delta) is written here by CTA 0 (or null)
   float eps;
   int paired;                // nibble order of the packed words: 0 reference, 1 paired (q4_common.cuh)
+  RopeOut rope;
   PeerReduce red;
 };
 
@@ -187,7 +202,12 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
             }
             unsigned char* st = ring + (size_t)s * kStageBytes;
             // out-of-range parts of a box are zero-filled and still counted in the byte total
-            if (is_w) {
+            if (p.rope.on) {
+              // tile = (128-row unit, 8 dims): rows {dim, half} = coordinates (.., (tile % 8) * 8, 0, tile / 8, ..)
+              mbar_arrive_expect_tx(&full[s], is_w ? kWBytes : kSBytes);
+              tma_load_5d_hint(is_w ? st : st + kWBytes, is_w ? &p.tm_w : &p.tm_s, 0, (tile & 7) * 8, 0, tile >> 3, k0 >> 8,
+                               &full[s], policy);
+            } else if (is_w) {
               mbar_arrive_expect_tx(&full[s], kWBytes);
               tma_load_3d_hint(st, &p.tm_w, 0, row0, k0 >> 8, &full[s], policy);
             } else {
@@ -208,9 +228,18 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
     pdl_wait();                                  // y may still be read by the previous kernel
     int rb = 0;
     uint32_t rround = 0;
+    const int rope_pos = (FAST && p.rope.on) ? *p.rope.pos : 0;
     for (int kb = 0; kb < nkb; ++kb) {
       int slot = 0;
       for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++slot) {
+        // rotary mode: lane 2r holds row r of the tile = dim (tile % 8) * 8 + r % 8 of half r / 8 of unit tile / 8;
+        // its cosine and sine are fetched before the wait for the partial sums
+        float rope_c = 1.f, rope_s = 0.f;
+        if (FAST && p.rope.on && (tile >> 3) < 2 * p.rope.nh) {
+          const int i = (tile & 7) * 8 + ((lane >> 1) & 7);
+          rope_c = p.rope.cos_t[(int64_t)rope_pos * 64 + i];
+          rope_s = p.rope.sin_t[(int64_t)rope_pos * 64 + i];
+        }
         if (!mbar_try_wait(&red_full[rb], rround & 1)) {
           if (!*(volatile int*)&s_abort && !mbar_wait_ns_relaxed(&red_full[rb], rround & 1, kProducerWaitNs)) {
             atomicExch(&g_gemv_pipe_error, 4);
@@ -230,7 +259,20 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
             if (kb > 0) sum += *a;
             if (kb < nkb - 1) *a = sum;
           }
-          if (kb == nkb - 1) {
+          if (FAST && p.rope.on) {
+            // (one K block, one batch column: checked by the launcher)  q | k rows: rotate with the partner (row r ^ 8
+            // = lane ^ 16) on the fp16-rounded matmul results, as the separate kernel does; v rows: copy.
+            const float vr = __half2float(__float2half_rn(sum));
+            const float pv = __shfl_xor_sync(0xffffffffu, vr, 16);
+            if ((lane & 1) == 0) {
+              const int r = lane >> 1, u = tile >> 3, nh = p.rope.nh;
+              const int d = (tile & 7) * 8 + (r & 7) + (r < 8 ? 0 : 64);
+              const float rot = r < 8 ? vr * rope_c - pv * rope_s : vr * rope_c + pv * rope_s;
+              if (u < nh) p.rope.q_out[u * 128 + d] = __float2half_rn(rot);
+              else if (u < 2 * nh) p.rope.k_cache[((int64_t)rope_pos * nh + (u - nh)) * 128 + d] = __float2half_rn(rot);
+              else p.rope.v_cache[((int64_t)rope_pos * nh + (u - 2 * nh)) * 128 + d] = __float2half_rn(vr);
+            }
+          } else if (kb == nkb - 1) {
             int row, col;
             if (FAST) {
               row = tile * kRows + e / NCP;      // [row][column] as the consumers stored it
@@ -815,6 +857,7 @@ struct Prologue {
   const __half* norm_w = nullptr;
   __half* x_out = nullptr;
   float eps = 0.f;
+  RopeOut rope;          // rotary embedding + KV append in the epilogue (qkv matmul of a batch-1 step)
 };
 
 template <int NC, int CW, int CH, int PRO, bool FAST>
@@ -827,7 +870,23 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   constexpr int kThreads = (CW + 2) * 32;
   using XL = XLayout<NC>;
   PipeParams p;
-  {
+  p.rope = pro.rope;
+  if (pro.rope.on) {
+    // the fast form's epilogue layout, one K block, whole 128-row units
+    if (!FAST || NC != 1 || M != 1 || N % 128 != 0 || N != 3 * pro.rope.nh * 128) return B200_ENOTREADY;
+    // rows as {dim in half: 64 | half: 2 | unit: N/128}, tile = 8 dims x 2 halves of one unit
+    const uint64_t wd[5] = {32, 64, 2, (uint64_t)(N / 128), (uint64_t)(K / 256)};
+    const uint64_t ws[4] = {(uint64_t)K / 2, (uint64_t)K / 2 * 64, (uint64_t)K / 2 * 128, 128};
+    const uint32_t wb[5] = {32, 8, 2, 1, CH};
+    int rc = make_tmap(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 5, wq, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const uint64_t rp = (uint64_t)(K / 32) * 2;    // bytes per row of scales
+    const uint64_t sd[5] = {8, 64, 2, (uint64_t)(N / 128), (uint64_t)(K / 256)};
+    const uint64_t ss[4] = {rp, rp * 64, rp * 128, 16};
+    const uint32_t sb[5] = {8, 8, 2, 1, CH};
+    rc = make_tmap(&p.tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, scales, sd, ss, sb, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  } else {
     const uint64_t wd[3] = {32, (uint64_t)N, (uint64_t)(K / 256)};
     const uint64_t ws[2] = {(uint64_t)K / 2, 128};
     const uint32_t wb[3] = {32, kRows, CH};
@@ -938,6 +997,7 @@ int launch_pipe(const __half* x, const uint32_t* wq, const __half* scales, __hal
   }
   p.nstages = stages;
   p.kblk = kblk;
+  if (pro.rope.on && kblk < kpad) return B200_ENOTREADY;   // (K cut into blocks: the rotary epilogue takes one)
 
   cudaError_t e;
   cudaLaunchConfig_t cfg = {};
@@ -1106,6 +1166,21 @@ int launch_gemv_pipe_rmsnorm(const __half* x, const __half* delta, const __half*
   Prologue pro;
   pro.kind = kPrologueRmsNorm; pro.delta = delta; pro.norm_w = norm_w; pro.x_out = x_out; pro.eps = eps;
   return dispatch_pipe(x, wq, scales, y, M, N, K, stream, pro, PeerReduce{});
+}
+
+// qkv = rmsnorm(x + delta) . decode(W)^T for ONE row, with the rotary embedding and the KV append in the epilogue:
+// writes the rotated query to q_out and the new token's rotated key and value into the caches at *pos; no qkv
+// buffer.  B200_ENOTREADY when the launch would not use the fast form (the epilogue is written for its layout).
+int launch_gemv_pipe_rmsnorm_rope(const __half* x, const __half* delta, const __half* norm_w, __half* x_out, float eps,
+                                  const uint32_t* wq, const __half* scales, const float* cos_t, const float* sin_t,
+                                  const int* pos, __half* q_out, __half* k_cache, __half* v_cache, int64_t nh, int64_t K,
+                                  cudaStream_t stream) {
+  Prologue pro;
+  pro.kind = kPrologueRmsNorm; pro.delta = delta; pro.norm_w = norm_w; pro.x_out = x_out; pro.eps = eps;
+  pro.rope.cos_t = cos_t; pro.rope.sin_t = sin_t; pro.rope.pos = pos;
+  pro.rope.q_out = q_out; pro.rope.k_cache = k_cache; pro.rope.v_cache = v_cache;
+  pro.rope.nh = (int)nh; pro.rope.on = 1;
+  return dispatch_pipe(x, wq, scales, q_out /* unused */, 1, 3 * nh * 128, K, stream, pro, PeerReduce{});
 }
 
 // y = (silu(gu[:, :K]) * gu[:, K:]) . decode(W)^T

@@ -57,6 +57,10 @@ int launch_gemv(const __half* x, const uint32_t* wq, const __half* scales, __hal
 int launch_gemv_pipe_rmsnorm(const __half* x, const __half* delta, const __half* norm_w, __half* x_out, float eps,
                              const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N, int64_t K,
                              cudaStream_t stream);
+int launch_gemv_pipe_rmsnorm_rope(const __half* x, const __half* delta, const __half* norm_w, __half* x_out, float eps,
+                                  const uint32_t* wq, const __half* scales, const float* cos_t, const float* sin_t,
+                                  const int* pos, __half* q_out, __half* k_cache, __half* v_cache, int64_t nh, int64_t K,
+                                  cudaStream_t stream);
 int launch_gemv_pipe_swiglu(const __half* gu, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,
                             int64_t K, cudaStream_t stream);
 int launch_gemv_pipe_allreduce(const __half* x, const uint32_t* wq, const __half* scales, __half* y, int64_t M, int64_t N,

@@ -27,9 +27,10 @@ int make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void*
               CUtensorMapL2promotion promo) {
   std::call_once(g_once, resolve);
   if (!g_encode) return fail(B200_ENODEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t d[3];
-  cuuint64_t s[2];
-  cuuint32_t b[3], e[3];
+  if (rank < 1 || rank > 5) return fail(B200_EINVAL, "tensor map rank %d outside 1..5", rank);
+  cuuint64_t d[5] = {0, 0, 0, 0, 0};
+  cuuint64_t s[4] = {0, 0, 0, 0};
+  cuuint32_t b[5] = {0, 0, 0, 0, 0}, e[5] = {1, 1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) {
     d[i] = dims[i];
     b[i] = box[i];

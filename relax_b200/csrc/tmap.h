@@ -7,7 +7,7 @@
 
 namespace b200 {
 
-// Up to 3 dimensions, innermost first.  strides_bytes[i] is the byte stride of dimension i+1
+// Up to 5 dimensions, innermost first.  strides_bytes[i] is the byte stride of dimension i+1
 // (dimension 0 is dense).  Returns 0 or a negative B200_E* code (message stored).
 int make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
               const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,

@@ -103,7 +103,7 @@ class DecodeEngine:
 
     def __init__(self, cfg: DecoderConfig, layers, embed, final_norm, lm_head, batch: int, max_ctx: int,
                  device, rank: int = 0, world: int = 1, group=None, fused=None, peer_reduce: bool = True,
-                 fused_attention=False, guard=None, verify: bool = True, layer_kernel=None):
+                 fused_attention=False, guard=None, verify: bool = True, layer_kernel=None, rope_epilogue: bool = True):
         self.cfg, self.batch, self.max_ctx, self.device = cfg, batch, max_ctx, torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         self.layers, self.embed, self.final_norm, self.lm_head = layers, embed, final_norm, lm_head
@@ -158,6 +158,9 @@ class DecodeEngine:
         # token) and slower on two (2.07 against 1.89), because every stage boundary inside it costs what a
         # dependent launch costs, and its attention stage has only eight warps per SM with loads in flight
         self.layer_kernel = False if layer_kernel is None else bool(layer_kernel)
+        # batch 1, fused prologues, three-launch attention: rotary embedding + KV append run in the epilogue of the
+        # qkv matmul (b200_q4f16_gemv_rmsnorm_rope), one launch less per layer
+        self.rope_epilogue = bool(rope_epilogue) and self.fused and B == 1 and not self.fused_attention and not self.layer_kernel
         if self.layer_kernel and B != 1:
             raise ValueError("the one-kernel-per-layer path is the batch-1 path")
         # tensor parallel: the sum over ranks after o and down runs over NVLink peer memory, inside those matmul
@@ -266,7 +269,21 @@ class DecodeEngine:
         cfg, L, B, w = self.cfg, self.L, self.batch, self.layers[i]
         H, hl, il = cfg.hidden, cfg.hidden // self.world, w["inter_local"]
         dptr = delta.data_ptr() if delta is not None else None
-        if self.fused:
+        roped = False
+        if self.fused and self.rope_epilogue:
+            # residual stream: x --(+delta)--> x2 --(+o)--> x; rotary embedding and KV append in the matmul's epilogue
+            rc = L.b200_q4f16_gemv_rmsnorm_rope(self.x.data_ptr(), dptr, w["norm1"].data_ptr(), self.x2.data_ptr(), cfg.eps,
+                                                w["qkv"][0].data_ptr(), w["qkv"][1].data_ptr(), self.cos.data_ptr(),
+                                                self.sin.data_ptr(), self.pos.data_ptr(), self.q.data_ptr(),
+                                                self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.nh_local, H, sp)
+            if rc == _lib.ENOTREADY:
+                self.rope_epilogue = False      # (the exact form is selected: two kernels from now on)
+            else:
+                self._check(rc)
+                roped = True
+        if roped:
+            pass
+        elif self.fused:
             # residual stream: x --(+delta)--> x2 --(+o)--> x
             self._check(L.b200_q4f16_gemv_rmsnorm(self.x.data_ptr(), dptr, w["norm1"].data_ptr(), self.x2.data_ptr(), cfg.eps,
                                                   w["qkv"][0].data_ptr(), w["qkv"][1].data_ptr(), self.qkv.data_ptr(),
@@ -274,7 +291,15 @@ class DecodeEngine:
         else:
             self._check(L.b200_rmsnorm(self.x.data_ptr(), dptr, w["norm1"].data_ptr(), self.h.data_ptr(), B, H, cfg.eps, sp))
             self._matmul(self.h, w["qkv"], self.qkv, 3 * hl, H, sp)
-        if self.fused_attention == "rope":
+        if roped:
+            # The position and the older cache entries were final before the matmul in front began (the position was
+            # advanced two launches before this step's first kernel, each of which waits before it lets the next
+            # one start; the matmul's epilogue writes only the new token's slot, which the attention reads after
+            # its own wait)
+            self._check(L.b200_attn_decode(self.q.data_ptr(), self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.pos.data_ptr(),
+                                           self.attn.data_ptr(), self.scratch.data_ptr(), B, self.nh_local, self.max_ctx,
+                                           _lib.ATTN_EARLY_KV_LOADS, sp))
+        elif self.fused_attention == "rope":
             # rotary embedding + KV append + per-chunk attention in one launch, the merge in a second
             self._check(L.b200_attn_decode_rope(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
                                                 self.kc[i].data_ptr(), self.vc[i].data_ptr(), self.attn.data_ptr(),
@@ -374,7 +399,10 @@ class DecodeEngine:
         head = 1 if self.lm_head is not None and self.batch <= 16 else 0
         if self.layer_kernel:
             return 1 + len(self.layers) + 1 + head + 2
-        return 1 + len(self.layers) * ((5 if self.fused else 9) + (1 if self.fused_attention == "rope" else (0 if self.fused_attention else 2))) + 1 + head + 2
+        per_layer = (5 if self.fused else 9) + (1 if self.fused_attention == "rope" else (0 if self.fused_attention else 2))
+        if self.rope_epilogue:
+            per_layer -= 1
+        return 1 + len(self.layers) * per_layer + 1 + head + 2
 
     def capture(self, stream):
         """Captures one step into a CUDA graph on `stream` (after one eager warm-up step, which

@@ -5,7 +5,7 @@ import torch
 
 import oracle
 from oracle import decoder as odec
-from relax_b200 import _lib, decoder, tp
+from relax_b200 import _lib, decoder, synth, tp
 
 pytestmark = pytest.mark.gpu
 
@@ -331,3 +331,51 @@ def test_lm_head_argument_checks(cuda_lib):
     assert L.b200_lm_head(p, p, None, p, None, 1, 4, 32, 0, 0) == _lib.EINVAL and "scratch" in _lib.last_error()
     assert L.b200_lm_head(p + 2, p, p, None, None, 1, 4, 32, 0, 0) == _lib.EINVAL
     assert L.b200_lm_head(p, p, p, None, None, 16, 4, 65536, 0, 0) == _lib.EINVAL and "shared memory" in _lib.last_error()
+
+
+@pytest.mark.parametrize("nh,K,with_delta", [(32, 4096, True), (4, 4096, False), (2, 8192, True), (12, 3584, True)])
+def test_qkv_matmul_with_rotary_epilogue_equals_the_two_kernels(cuda_lib, nh, K, with_delta):
+    """b200_q4f16_gemv_rmsnorm_rope against b200_q4f16_gemv_rmsnorm followed by b200_rope_kv_append: the same
+    arithmetic, so the rotated query, the cache slot of the new token and the updated residual stream agree bit
+    for bit; nothing else in the caches is touched."""
+    N, max_ctx, pos = 3 * nh * 128, 24, 17
+    rng = np.random.default_rng(nh + K)
+    x, wq, s = synth.make_case(1, N, K, seed=nh * 3 + 1)
+    delta = (0.1 * rng.standard_normal((1, K))).astype(np.float16)
+    norm = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    tx, twq, ts, td, tn = (dev(a) for a in (x, wq, s, delta, norm))
+    dptr = td.data_ptr() if with_delta else None
+    cos, sin = decoder.rope_tables(max_ctx, 128, 10000.0, "cuda")
+    tpos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    fill = torch.from_numpy(rng.standard_normal((max_ctx, nh, 128)).astype(np.float16)).cuda()
+    out = {}
+    for name in ("two", "one"):
+        kc, vc = fill.clone(), (fill * 0.5).clone()
+        q = torch.zeros(nh * 128, dtype=torch.float16, device="cuda")
+        xo = torch.zeros(1, K, dtype=torch.float16, device="cuda")
+        if name == "two":
+            qkv = torch.zeros(1, N, dtype=torch.float16, device="cuda")
+            assert cuda_lib.b200_q4f16_gemv_rmsnorm(tx.data_ptr(), dptr, tn.data_ptr(), xo.data_ptr(), 1e-5, twq.data_ptr(),
+                                                    ts.data_ptr(), qkv.data_ptr(), 1, N, K, 0) == 0, _lib.last_error()
+            assert cuda_lib.b200_rope_kv_append(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), tpos.data_ptr(), q.data_ptr(),
+                                                kc.data_ptr(), vc.data_ptr(), 1, nh, max_ctx, 0) == 0, _lib.last_error()
+        else:
+            rc = cuda_lib.b200_q4f16_gemv_rmsnorm_rope(tx.data_ptr(), dptr, tn.data_ptr(), xo.data_ptr(), 1e-5, twq.data_ptr(),
+                                                       ts.data_ptr(), cos.data_ptr(), sin.data_ptr(), tpos.data_ptr(),
+                                                       q.data_ptr(), kc.data_ptr(), vc.data_ptr(), nh, K, 0)
+            assert rc == 0, (rc, _lib.last_error())
+        torch.cuda.synchronize()
+        out[name] = [t.cpu().numpy().view(np.uint16) for t in (q, kc, vc, xo)]
+    for a, b, what in zip(out["one"], out["two"], ("q", "k cache", "v cache", "x_out")):
+        assert np.array_equal(a, b), what
+    assert cuda_lib.b200_device_error_flags() == 0
+    # the exact form has another epilogue layout: the entry point says so and launches nothing
+    _lib.set_option("gemv.exact", 1)
+    try:
+        q = torch.zeros(nh * 128, dtype=torch.float16, device="cuda")
+        rc = cuda_lib.b200_q4f16_gemv_rmsnorm_rope(tx.data_ptr(), dptr, tn.data_ptr(), None, 1e-5, twq.data_ptr(), ts.data_ptr(),
+                                                   cos.data_ptr(), sin.data_ptr(), tpos.data_ptr(), q.data_ptr(),
+                                                   fill.data_ptr(), fill.data_ptr(), nh, K, 0)
+        assert rc == _lib.ENOTREADY
+    finally:
+        _lib.set_option("gemv.exact", 0)

@@ -54,16 +54,19 @@ def _worker(rank, world, port, ret, hidden, heads, inter):
         # "peer-wide": 12 rows (the first two sequences repeated), above the range of the matmul kernel with the sum
         # inside it: mid-batch matmul into the peer-mapped buffer + b200_allreduce_peer
         wide = 12
+        # "peer-one": batch 1 through the separate kernels (fused prologues, rotary embedding in the qkv matmul's epilogue,
+        # sums over ranks inside the o / down matmuls)
         for name, w, peer in (("single", 1, False), ("nccl", world, False), ("peer", world, True), ("layer", world, True),
-                              ("peer-wide", world, True)):
+                              ("peer-wide", world, True), ("peer-one", world, True)):
             r = 0 if w == 1 else rank
-            nb = 1 if name == "layer" else wide if name == "peer-wide" else B
+            nb = 1 if name in ("layer", "peer-one") else wide if name == "peer-wide" else B
             layers = [decoder.to_device(tp.shard_layer(l, r, w, cfg.hidden, cfg.inter), dev) for l in full]
             vl = cfg.vocab // w
             eng = decoder.DecodeEngine(cfg, layers, embed, fnorm, embed[r * vl:(r + 1) * vl].contiguous(), nb, max_ctx, dev,
                                        rank=r, world=w, peer_reduce=peer, layer_kernel=(name == "layer"))
             assert (eng.peer is not None) == peer and eng.layer_kernel == (name == "layer")
             assert (nb > eng.PEER_FUSED_MAX_ROWS) == (name == "peer-wide")
+            assert eng.rope_epilogue == (name == "peer-one")
             rows = [j % B for j in range(nb)]           # which of the oracle's sequences each row repeats
             eng.tokens.copy_(torch.tensor([tokens[j] for j in rows], dtype=torch.int32))
             hs, ls = [], []
@@ -79,7 +82,7 @@ def _worker(rank, world, port, ret, hidden, heads, inter):
             dist.barrier()
         if rank == 0:
             errs = {}
-            for name in ("single", "nccl", "peer", "layer", "peer-wide"):
+            for name in ("single", "nccl", "peer", "layer", "peer-wide", "peer-one"):
                 e_or, e_l = 0.0, 0.0
                 nb = results[name][0][0].shape[0]
                 rows = [j % B for j in range(nb)]
