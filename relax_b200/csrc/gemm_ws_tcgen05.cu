@@ -1,5 +1,6 @@
 // Weight-stationary q4f16 matmul on the 5th-generation tensor cores for mid-sized batches
-// (16 < M <= 128, and M = 9..16 where it beats the skinny kernel): y[M,N] = x[M,K] . decode(Wq,S)^T.
+// (M <= 128; the dispatcher gives it 17..128 rows, and 9..16 where it beats the skinny kernel):
+// y[M,N] = x[M,K] . decode(Wq,S)^T.
 //
 // Decode at batch 16..128 is still bound by streaming the weights once, so the roles of the prefill
 // kernel are swapped: the MMA's M dimension is 128 WEIGHT rows (A operand = dequantised weights), its
@@ -8,8 +9,9 @@
 // tiles through distributed shared memory in rank order (deterministic), so small N still fills
 // the GPU (N = 4096: 32 row tiles x 4 K slices = 128 CTAs) without atomics or a scratch buffer.
 //
-//   warp 0      TMA producer: x block {64 k, NB batch rows} (128-byte swizzle), packed weights
-//               {16 words = 128 k, 128 rows} (64-byte swizzle), scales {8 groups = 256 k, 128 rows}
+//   warps 0,2,3 TMA producers: x (WK K blocks of {64 k, NB batch rows} per load, 128-byte swizzle), packed
+//               weights (256 k per load: whole 128-byte lines of 128 rows, 128-byte swizzle), scales
+//               {8 groups = 256 k, 128 rows}; the first ring-full of weights is requested during set-up
 //   warps 8-23  dequantisers, two groups of 8 warps that take alternate 256-k spans (a group's load ->
 //               convert -> store -> fence -> arrive chain is latency bound; two chains in flight double
 //               the rate): thread (row, half) turns 4 packed words of one scale group into 32 fp16
