@@ -172,3 +172,50 @@ def test_weight_file_format_cpu(tmp_path):
     open(bad, "wb").write(raw[:-100])
     with pytest.raises(weights_io.FormatError):
         weights_io.load(bad)
+
+
+def test_argument_checks_of_the_newer_entry_points_need_no_gpu():
+    """Validation comes before any device call: bad arguments give B200_EINVAL with a message on a box without a
+    GPU; well-formed calls then fail with B200_ENODEVICE there (never a silent success)."""
+    import ctypes
+
+    import torch
+
+    L = _lib.lib()
+    buf = torch.zeros(4096, dtype=torch.int32)
+    p = buf.data_ptr()
+    no_gpu = not torch.cuda.is_available()
+    # offline repack
+    assert L.b200_q4f16_repack(p, p, 2, 256, 7, None) == _lib.EINVAL and "layout" in _lib.last_error()
+    assert L.b200_q4f16_repack(p, p, 2, 40, 1, None) == _lib.EINVAL
+    assert L.b200_q4f16_unpack(p, p + 16, 2, 256, 1, None) == _lib.EINVAL and "overlap" in _lib.last_error()
+    assert L.b200_q4f16_matmul_layout(p, p, p, p, 1, 2, 256, 9, None) == _lib.EINVAL
+    assert L.b200_set_option(b"weights.layout", 2) == _lib.EINVAL
+    assert L.b200_set_option(b"gemv.exact", 3) == _lib.EINVAL
+    if no_gpu:
+        assert L.b200_q4f16_repack(p, p, 2, 256, 1, None) == _lib.ENODEVICE
+    # output projection
+    assert L.b200_lm_head(p, p, p, None, None, 17, 4, 32, 0, None) == _lib.EINVAL and "16 rows" in _lib.last_error()
+    assert L.b200_lm_head(p, p, p, None, None, 1, 4, 48, 0, None) == _lib.EINVAL
+    assert L.b200_lm_head(p, p, None, p, None, 1, 4, 32, 0, None) == _lib.EINVAL and "scratch" in _lib.last_error()
+    if no_gpu:
+        assert L.b200_lm_head(p, p, p, None, None, 1, 4, 32, 0, None) == _lib.ENODEVICE
+        assert L.b200_lm_head_scratch_bytes() == -1
+    # sum over ranks as its own kernel
+    d = _lib.PeerReduce()
+    assert L.b200_allreduce_peer(12, ctypes.byref(d), None) == _lib.EINVAL and "multiple of 8" in _lib.last_error()
+    assert L.b200_allreduce_peer(16, None, None) == _lib.EINVAL
+    d.world, d.rank = 1, 0
+    assert L.b200_allreduce_peer(16, ctypes.byref(d), None) == _lib.EINVAL and "world" in _lib.last_error()
+    d.world, d.rank = 2, 0
+    assert L.b200_allreduce_peer(16, ctypes.byref(d), None) == _lib.EINVAL      # no epoch / out / peers
+    d.epoch, d.out = p, p
+    d.peer_y[0], d.peer_flags[0] = p, p
+    assert L.b200_allreduce_peer(16, ctypes.byref(d), None) == _lib.EINVAL and "peer 1" in _lib.last_error()
+    # qkv matmul with the rotary epilogue
+    args = [p, None, p, None, 1e-5, p, p, p, p, p, p, p, p]
+    assert L.b200_q4f16_gemv_rmsnorm_rope(*args, 0, 256, None) == _lib.EINVAL and "heads" in _lib.last_error()
+    assert L.b200_q4f16_gemv_rmsnorm_rope(*args, 2, 200, None) == _lib.EINVAL
+    assert L.b200_q4f16_gemv_rmsnorm_rope(*(args[:7] + [None] + args[8:]), 2, 256, None) == _lib.EINVAL
+    if no_gpu:
+        assert L.b200_q4f16_gemv_rmsnorm_rope(*args, 2, 256, None) == _lib.ENODEVICE
