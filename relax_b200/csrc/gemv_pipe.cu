@@ -1021,9 +1021,10 @@ int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __h
                   cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   if (m == 1) {
     // batch 1: the fast form unless the caller asks for the reference's rounding of every weight (gemv.exact = 1)
-    // or, by default (gemv.exact = 0), K fills its last 4096-k stage poorly.  The fast form holds its first stage in
-    // registers BEFORE it stages x, so the arrival of the weights and the staging of x follow one another, which a
-    // short kernel does not win back: measured at N = 4096, exact / fast = 2.86 / 3.70 us at K = 512, 3.28 / 3.90 at
+    // or, by default (gemv.exact = 0), K fills its last 4096-k stage poorly.  The fast form has about 0.7 us more fixed
+    // cost per launch (its staging of x also builds the offset sums and the block-diagonal operand) and only wins
+    // that back where there is a stage's worth of arithmetic to save; taking its first stage into registers only
+    // when it has already landed, instead of waiting for it, was measured too and changes nothing.  At N = 4096, exact / fast = 2.86 / 3.70 us at K = 512, 3.28 / 3.90 at
     // 1536, 5.45 / 6.08 at 4608, 5.87 / 6.24 at 5632, against 4.55 / 4.35 at 3584, 4.88 / 4.49 at 4096, 7.07 / 6.67 at
     // 8192, 8.94 / 8.73 at 11008.  gemv.exact = 2 forces the fast form for every K (tests).
     const int stages = (k + CH * 256 - 1) / (CH * 256);
