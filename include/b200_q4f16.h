@@ -206,8 +206,8 @@ B200_API int b200_q4f16_gemv_rmsnorm(const void* x, const void* delta, const voi
  * [max_pos, 64], position *pos) into q_out fp16 [heads*128], the rotated key and the value of the new token go
  * into k_cache / v_cache fp16 [max_ctx, heads, 128] at slot *pos; there is no qkv buffer.  Same arithmetic as the
  * two separate kernels (the rotation works on the fp16-rounded matmul results).  Returns B200_ENOTREADY, with
- * nothing launched, when this launch would not use the skinny kernel's fast form (option gemv.exact = 1, or a K
- * that fills its stages poorly): call the two separate entry points then. */
+ * nothing launched, when this launch would not use the skinny kernel's fast form (option gemv.exact = 1, or K below
+ * 2560): call the two separate entry points then. */
 B200_API int b200_q4f16_gemv_rmsnorm_rope(const void* x, const void* delta, const void* norm_w, void* x_out, float eps,
                                           const void* wq, const void* scales, const void* cos_t, const void* sin_t,
                                           const void* pos, void* q_out, void* k_cache, void* v_cache, int64_t heads,

@@ -111,6 +111,68 @@ struct PipeParams {
   PeerReduce red;
 };
 
+// The arithmetic of the fast form over the first NU of a warp's U chunks of one stage (see the comment at its call
+// site in the kernel).  NU < U: the other chunks lie past K (zero-filled) and are skipped, so a short K costs what it
+// holds and not a whole stage.
+template <int NU, int U, int MT, int kXUnit, int kCUnit>
+__device__ __forceinline__ void fast_stage_fn(float (&acc)[2][MT][4], const uint4 (&w)[U][2][2], const uint2 (&sc)[U][2],
+                                            const uint4* xb, int x_mul, const float4* cu, const Q4Consts& qc,
+                                            uint32_t magic_hi) {
+  float d[U][2][4];
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    uint32_t a[U][2][8];      // raw (offset) nibble pairs: [0..3] first MMA (rows g, g+8: even k, odd k), [4..7] second
+    uint4 b[U][2];
+#pragma unroll
+    for (int u = 0; u < NU; ++u)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t w0 = wd == 0 ? w[u][0][h].x : wd == 1 ? w[u][0][h].y : wd == 2 ? w[u][0][h].z : w[u][0][h].w;
+        const uint32_t w1 = wd == 0 ? w[u][1][h].x : wd == 1 ? w[u][1][h].y : wd == 2 ? w[u][1][h].z : w[u][1][h].w;
+        b[u][h] = xb[x_mul * (u * kXUnit + 4 * h + wd)];      // (lanes that own no column all read one zero slot)
+        a[u][h][0] = lop3_and_or(w0, qc.lo, qc.magic);
+        a[u][h][1] = lop3_and_or(w1, qc.lo, qc.magic);
+        a[u][h][2] = lop3_and_or(w0, qc.hi, magic_hi);
+        a[u][h][3] = lop3_and_or(w1, qc.hi, magic_hi);
+        const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+        a[u][h][4] = lop3_and_or(w0s, qc.lo, qc.magic);
+        a[u][h][5] = lop3_and_or(w1s, qc.lo, qc.magic);
+        a[u][h][6] = lop3_and_or(w0s, qc.hi, magic_hi);
+        a[u][h][7] = lop3_and_or(w1s, qc.hi, magic_hi);
+      }
+#pragma unroll
+    for (int u = 0; u < NU; ++u)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (wd == 0) {
+          const float4 c = cu[u * kCUnit + h];
+          mma_16x8x16_c(d[u][h], a[u][h][0], a[u][h][1], a[u][h][2], a[u][h][3], b[u][h].x, b[u][h].y, c.x, c.y, c.z, c.w);
+        } else {
+          mma_16x8x16(d[u][h], a[u][h][0], a[u][h][1], a[u][h][2], a[u][h][3], b[u][h].x, b[u][h].y);
+        }
+      }
+#pragma unroll
+    for (int u = 0; u < NU; ++u)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        mma_16x8x16(d[u][h], a[u][h][4], a[u][h][5], a[u][h][6], a[u][h][7], b[u][h].z, b[u][h].w);
+  }
+#pragma unroll
+  for (int u = 0; u < NU; ++u) {
+    // scales of groups 4t'+0..3: (s0, s1) (s2, s3); even groups belong to set 0, odd ones to set 1
+    const float2 g01 = __half22float2(u32_as_h2(sc[u][0].x)), g23 = __half22float2(u32_as_h2(sc[u][0].y));
+    const float2 h01 = __half22float2(u32_as_h2(sc[u][1].x)), h23 = __half22float2(u32_as_h2(sc[u][1].y));
+    acc[0][0][0] = fmaf(g01.x, d[u][0][0], acc[0][0][0]);
+    acc[0][0][0] = fmaf(g23.x, d[u][0][1], acc[0][0][0]);
+    acc[1][0][0] = fmaf(g01.y, d[u][1][0], acc[1][0][0]);
+    acc[1][0][0] = fmaf(g23.y, d[u][1][1], acc[1][0][0]);
+    acc[0][0][2] = fmaf(h01.x, d[u][0][2], acc[0][0][2]);
+    acc[0][0][2] = fmaf(h23.x, d[u][0][3], acc[0][0][2]);
+    acc[1][0][2] = fmaf(h01.y, d[u][1][2], acc[1][0][2]);
+    acc[1][0][2] = fmaf(h23.y, d[u][1][3], acc[1][0][2]);
+  }
+}
+
 // Shared memory carve-up (after rounding the base up to 1024 bytes):
 //   ring:  nstages * kStageBytes
 //   bars:  full[kMaxStages] empty[kMaxStages] red_full[kMaxStages+1] red_empty[kMaxStages+1]
@@ -394,61 +456,11 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
   // minus the offset sums.  Afterwards d[u][h][0], [1] are row g's sums over groups 4t+h and 4t+2+h, [2], [3] row
   // g+8's.  The MMAs are issued round-robin over the 2U accumulators (an MMA that follows the one it depends on
   // waits out the tensor pipe's whole latency; with the accumulators interleaved nothing waits).
-  auto fast_stage = [&](const uint4 (&w)[U][2][2], const uint2 (&sc)[U][2], const uint4* xu, const float4* cu) {
-    float d[U][2][4];
+  auto fast_stage = [&](int nu, const uint4 (&w)[U][2][2], const uint2 (&sc)[U][2], const uint4* xu, const float4* cu) {
+    static_assert(!FAST || U == 2, "the dispatch below lists the chunk counts of U = 2");
     const uint4* xb = x_own ? xu : &s_zero;
-#pragma unroll
-    for (int wd = 0; wd < 4; ++wd) {
-      uint32_t a[U][2][8];      // raw (offset) nibble pairs: [0..3] first MMA (rows g, g+8: even k, odd k), [4..7] second
-      uint4 b[U][2];
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t w0 = wd == 0 ? w[u][0][h].x : wd == 1 ? w[u][0][h].y : wd == 2 ? w[u][0][h].z : w[u][0][h].w;
-          const uint32_t w1 = wd == 0 ? w[u][1][h].x : wd == 1 ? w[u][1][h].y : wd == 2 ? w[u][1][h].z : w[u][1][h].w;
-          b[u][h] = xb[x_mul * (u * kXUnit + 4 * h + wd)];      // (lanes that own no column all read one zero slot)
-          a[u][h][0] = lop3_and_or(w0, qc.lo, qc.magic);
-          a[u][h][1] = lop3_and_or(w1, qc.lo, qc.magic);
-          a[u][h][2] = lop3_and_or(w0, qc.hi, magic_hi);
-          a[u][h][3] = lop3_and_or(w1, qc.hi, magic_hi);
-          const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
-          a[u][h][4] = lop3_and_or(w0s, qc.lo, qc.magic);
-          a[u][h][5] = lop3_and_or(w1s, qc.lo, qc.magic);
-          a[u][h][6] = lop3_and_or(w0s, qc.hi, magic_hi);
-          a[u][h][7] = lop3_and_or(w1s, qc.hi, magic_hi);
-        }
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (wd == 0) {
-            const float4 c = cu[u * kCUnit + h];
-            mma_16x8x16_c(d[u][h], a[u][h][0], a[u][h][1], a[u][h][2], a[u][h][3], b[u][h].x, b[u][h].y, c.x, c.y, c.z, c.w);
-          } else {
-            mma_16x8x16(d[u][h], a[u][h][0], a[u][h][1], a[u][h][2], a[u][h][3], b[u][h].x, b[u][h].y);
-          }
-        }
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-          mma_16x8x16(d[u][h], a[u][h][4], a[u][h][5], a[u][h][6], a[u][h][7], b[u][h].z, b[u][h].w);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      // scales of groups 4t'+0..3: (s0, s1) (s2, s3); even groups belong to set 0, odd ones to set 1
-      const float2 g01 = __half22float2(u32_as_h2(sc[u][0].x)), g23 = __half22float2(u32_as_h2(sc[u][0].y));
-      const float2 h01 = __half22float2(u32_as_h2(sc[u][1].x)), h23 = __half22float2(u32_as_h2(sc[u][1].y));
-      acc[0][0][0] = fmaf(g01.x, d[u][0][0], acc[0][0][0]);
-      acc[0][0][0] = fmaf(g23.x, d[u][0][1], acc[0][0][0]);
-      acc[1][0][0] = fmaf(g01.y, d[u][1][0], acc[1][0][0]);
-      acc[1][0][0] = fmaf(g23.y, d[u][1][1], acc[1][0][0]);
-      acc[0][0][2] = fmaf(h01.x, d[u][0][2], acc[0][0][2]);
-      acc[0][0][2] = fmaf(h23.x, d[u][0][3], acc[0][0][2]);
-      acc[1][0][2] = fmaf(h01.y, d[u][1][2], acc[1][0][2]);
-      acc[1][0][2] = fmaf(h23.y, d[u][1][3], acc[1][0][2]);
-    }
+    if (nu >= 2) fast_stage_fn<(U < 2 ? U : 2), U, MT, kXUnit, kCUnit>(acc, w, sc, xb, x_mul, cu, qc, magic_hi);
+    else if (nu == 1) fast_stage_fn<1, U, MT, kXUnit, kCUnit>(acc, w, sc, xb, x_mul, cu, qc, magic_hi);
   };
   // Fast form: this warp's share of stage `s` into registers; the stage goes back to the producer at once.
   auto fast_load = [&](int s, uint32_t round, uint4 (&w)[U][2][2], uint2 (&sc)[U][2]) {
@@ -726,8 +738,9 @@ q4f16_gemv_pipe_kernel(const __grid_constant__ PipeParams p) {
         if (FAST) {
           // (the first stage of the launch is in registers already)
           if (!(kb == 0 && tile == (int)blockIdx.x && k0 == k_lo)) fast_load(s, round, fw, fsc);
-          // chunks past K were zero-filled, their activations and offset sums staged as zeros: they add nothing
-          fast_stage(fw, fsc, xk, ck);
+          // this warp's chunks of the stage are warp and warp + CW; those past K are skipped
+          const int nch = (min(k_hi, k0 + KC) - k0 + 255) >> 8;
+          fast_stage((warp < nch) + (warp + CW < nch), fw, fsc, xk, ck);
         } else {
         // On a timeout the kernel keeps going without waiting (results are garbage, the error
         // flag says so) so that every warp still reaches the named barriers and the CTA ends.
@@ -1021,15 +1034,12 @@ int launch_pipe_m(const __half* x, const uint32_t* wq, const __half* scales, __h
                   cudaStream_t stream, const Prologue& pro, const PeerReduce& red) {
   if (m == 1) {
     // batch 1: the fast form unless the caller asks for the reference's rounding of every weight (gemv.exact = 1)
-    // or, by default (gemv.exact = 0), K fills its last 4096-k stage poorly.  The fast form has about 0.7 us more fixed
-    // cost per launch (its staging of x also builds the offset sums and the block-diagonal operand) and only wins
-    // that back where there is a stage's worth of arithmetic to save; taking its first stage into registers only
-    // when it has already landed, instead of waiting for it, was measured too and changes nothing.  At N = 4096, exact / fast = 2.86 / 3.70 us at K = 512, 3.28 / 3.90 at
-    // 1536, 5.45 / 6.08 at 4608, 5.87 / 6.24 at 5632, against 4.55 / 4.35 at 3584, 4.88 / 4.49 at 4096, 7.07 / 6.67 at
-    // 8192, 8.94 / 8.73 at 11008.  gemv.exact = 2 forces the fast form for every K (tests).
-    const int stages = (k + CH * 256 - 1) / (CH * 256);
-    const bool fills = (int64_t)k * 100 >= (int64_t)stages * CH * 256 * 85;
-    const bool fast = options().gemv_exact == 2 || (options().gemv_exact == 0 && fills);
+    // or, by default (gemv.exact = 0), K is short.  The fast form's staging of x also builds the offset sums and the
+    // block-diagonal operand, about 0.15 us more per launch, which it wins back from K of about 2500 on: measured at
+    // N = 4096, exact / fast = 2.96 / 3.12 us at K = 512, 3.38 / 3.51 at 1536, 3.62 / 3.69 at 2048, 4.16 / 4.13 at
+    // 2816, 4.88 / 4.58 at 4096, 7.26 / 6.80 at 8192, 9.16 / 8.72 at 11008 (and 14.3 / 12.9 at N = 22016, K = 4096).
+    // gemv.exact = 2 forces the fast form for every K (tests).
+    const bool fast = options().gemv_exact == 2 || (options().gemv_exact == 0 && k >= 2560);
     if (fast) return launch_pipe<1, CW, CH, PRO, true>(x, wq, scales, y, m, n, k, stream, pro, red);
     return launch_pipe<1, CW, CH, PRO, false>(x, wq, scales, y, m, n, k, stream, pro, red);
   }
